@@ -1,6 +1,7 @@
 """Typed configuration, the block-by-block model description, and the architecture registry."""
 from .spec import (BiasAttentionSpec, MlstmSpec, MoeSpec, PostNormBlockSpec)  # noqa: F401
 from .spec import (DeltaRuleSpec, LatentAttentionSpec, ParallelBlockSpec, RotaryPairsSpec, TokenSideSpec)  # noqa: F401
+from .spec import (LimitedMlpSpec, SigmoidAttentionSpec)  # noqa: F401
 from .spec import (AttentionSpec, BlockSpec, ConfigError, GatedMlpSpec, LinearHeadSpec, ModelSpec, NoPositionSpec,
                    RmsNormSpec, RotarySpec, ScheduleEntry)
 from .registry import (Architecture, architecture, architecture_of, known_architectures,
@@ -43,10 +44,24 @@ register_architecture(Architecture(
     complete_config=_lotilix.with_sizes_of,
 ))
 
+from . import mekevik as _mekevik
+from .mekevik import MekevikConfig
+
+register_architecture(Architecture(
+    name=_mekevik.ARCHITECTURE,
+    read_config=MekevikConfig.from_dict,
+    to_spec=MekevikConfig.to_spec,
+    tensor_name=_mekevik.tensor_name,
+    cap_positions=MekevikConfig.with_max_positions,
+    config_to_dict=MekevikConfig.to_dict,
+    complete_config=_mekevik.with_sizes_of,
+))
+
 __all__ = [
     "AttentionSpec", "BlockSpec", "ConfigError", "GatedMlpSpec", "LinearHeadSpec", "ModelSpec", "NoPositionSpec",
     "RmsNormSpec", "RotarySpec", "ScheduleEntry", "Architecture", "architecture", "architecture_of",
     "known_architectures", "read_config_json", "register_architecture", "unregister_architecture",
     "LlamaConfig", "FesoraxConfig", "BiasAttentionSpec", "MlstmSpec", "MoeSpec", "PostNormBlockSpec",
+    "MekevikConfig", "SigmoidAttentionSpec", "LimitedMlpSpec",
     "LotilixConfig", "DeltaRuleSpec", "LatentAttentionSpec", "ParallelBlockSpec", "RotaryPairsSpec", "TokenSideSpec",
 ]

@@ -116,6 +116,36 @@ class BiasAttentionSpec:
 
 
 @dataclass(frozen=True)
+class SigmoidAttentionSpec:
+    """Causal attention without a softmax: a visible key weighs sigmoid(q . k * scale + bias) and nothing is
+    normalised over the keys.  Grouped key/value heads with value heads of a width of their own; optionally an
+    RMS norm with a gain over the whole query projection and one over the whole key projection (all heads of a
+    token at once); a learned bias by log-bucketed distance; a bias per head inside the logistic function; the
+    heads' weights mixed by a learned matrix (weight_h <- sum_g M[h, g] weight_g, each head applying its mixed
+    weights to the values of its own key/value head); values blended with those of another layer
+    (``value_mix``: "source" keeps its values for later layers of the same ``value_group``, "blend" computes
+    v <- (1 - l) v + l v_source with a learned l and caches that); a logistic gate on every output number."""
+
+    width: int
+    n_heads: int
+    n_kv_heads: int
+    head_dim: int
+    v_head_dim: int
+    scale: float
+    window: int = 0  # 0: every earlier key; w > 0: the last w keys
+    whole_norm: bool = True  # RMS norms over the whole query and key projections, each with a gain
+    norm_eps: float = 1e-6
+    bias_buckets: int = 0  # rows of the distance-bias table; 0: no bias
+    bias_max_distance: int = 0  # the distance from which on the last bucket is used
+    head_bias: bool = True  # a learned number per head added to the score
+    head_mix: bool = True  # the heads' weights are mixed by a learned [heads, heads] matrix
+    value_mix: str = "none"  # "none" | "source" | "blend"
+    value_group: str = "v"  # layers that blend read the source of the same group
+    output_gate: bool = True  # the heads' outputs times the logistic function of a projection of the mixer's input
+    kind: str = "sigmoid_attention"
+
+
+@dataclass(frozen=True)
 class LatentAttentionSpec:
     """Softmax attention through low-rank latents: queries from a normed latent of ``q_rank`` numbers; per token
     one normed latent of ``kv_rank`` numbers, from which every head's unrotated keys (``head_dim``) and values
@@ -183,6 +213,10 @@ class MoeSpec:
     slope: float = 1.702  # the activation is g * sigmoid(slope * g) * (u + 1)
     weight_on_input: bool = True  # the router weight multiplies the expert's input (False: its output)
     renormalise: bool = False  # divide the chosen experts' weights by their sum
+    scores: str = "sigmoid"  # the router's scores: "sigmoid" of each logit, or "softmax" over all experts
+    weight_scale: float = 1.0  # factor on the (renormalised) weights
+    renormalise_eps: float = 0.0  # added to the sum the weights are divided by
+    activation: str = "limited"  # "limited": the clamped unit above; "silu" / "gelu_tanh": act(g) * u, no clamps
     kind: str = "moe"
 
 
@@ -195,6 +229,18 @@ class GatedMlpSpec:
     activation: str = "silu"  # or "gelu_tanh"
     wide_output: bool = False  # the delta leaves the last product in float32 instead of the compute type
     kind: str = "gated_mlp"
+
+
+@dataclass(frozen=True)
+class LimitedMlpSpec:
+    """Dense feed-forward with the clamped gated unit: down(g * sigmoid(slope g) * (u + 1)) with
+    g = min(gate x, limit), u = clamp(up x, -limit, limit)."""
+
+    width: int
+    intermediate: int
+    limit: float
+    slope: float = 1.702
+    kind: str = "limited_mlp"
 
 
 @dataclass(frozen=True)
@@ -240,12 +286,14 @@ class TokenSideSpec:
 @dataclass(frozen=True)
 class ParallelBlockSpec:
     """A block with one norm whose output both sublayers read: x <- x + (mixer(norm(x)) + ffn(norm(x))); then
-    ``side`` (optional), which adds an input of its own.  ``ffn`` may be None."""
+    ``side`` (optional), which adds an input of its own.  ``ffn`` may be None.  With ``ffn_norm`` the feed-forward
+    reads a second norm of the same x: x <- x + (mixer(norm(x)) + ffn(ffn_norm(x)))."""
 
     mixer: Any
     ffn: Any
     norm: Any
     side: Any = None
+    ffn_norm: Any = None
     kind: str = "parallel"
 
 

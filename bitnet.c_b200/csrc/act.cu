@@ -150,6 +150,32 @@ extern "C" int bn_glu_limited(const void* h, void* out, int dtype, int n_rows, i
   return BN_OK;
 }
 
+// The plain gated unit on rows that hold `inter` gate values and then `inter` up values: out = act(gate) * up.
+template <typename T>
+__global__ void glu_halves_kernel(const T* __restrict__ h, T* __restrict__ out, int inter, size_t total, int act) {
+  pdl_launch_dependents();
+  pdl_wait();
+  size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  size_t t = idx / inter;
+  size_t j = idx - t * inter;
+  out[idx] = from_f32<T>(glu_activation(to_f32<T>(h[t * 2 * inter + j]), act) * to_f32<T>(h[t * 2 * inter + inter + j]));
+}
+
+extern "C" int bn_glu_halves(const void* h, void* out, int dtype, int n_rows, int inter, int act, cudaStream_t stream) {
+  if (n_rows <= 0) return BN_OK;
+  if (inter <= 0 || !h || !out || (act != BN_ACT_SILU && act != BN_ACT_GELU_TANH)) return BN_ERR_BAD_ARG;
+  size_t total = (size_t)n_rows * inter;
+  unsigned blocks = (unsigned)((total + 255) / 256);
+  if (dtype == BN_F32)
+    BN_LAUNCH(glu_halves_kernel<float>, blocks, 256, 0, stream, (const float*)h, (float*)out, inter, total, act);
+  else if (dtype == BN_BF16)
+    BN_LAUNCH(glu_halves_kernel<__nv_bfloat16>, blocks, 256, 0, stream, (const __nv_bfloat16*)h, (__nv_bfloat16*)out, inter, total, act);
+  else
+    return BN_ERR_BAD_ARG;
+  return BN_OK;
+}
+
 // A gated row of a second embedding: out[t, j] = act(pre[t, j]) * table[tokens[t], col0 + j], j < dim.
 // pre [n, pre_stride] and out [n, dim] of type `dtype`; the table [vocab, table_stride] of type
 // `table_dtype`; an id outside the table gives zeros.

@@ -49,6 +49,7 @@ SOURCES: Dict[str, str] = {
     "moe": "moe.cu",
     "rotary_pairs": "rotary_pairs.cu",
     "delta_rule": "delta_rule.cu",
+    "sigmoid_attention": "sigmoid_attention.cu",
 }
 
 NVCC_FLAGS = [

@@ -23,7 +23,8 @@
 
 template <typename T, typename W>
 __global__ void moe_route_kernel(const T* __restrict__ h, int width, const W* __restrict__ w, int n_experts, int top,
-                                 int renormalise, int* __restrict__ ids, float* __restrict__ weights) {
+                                 int renormalise, int softmax, float weight_scale, float sum_eps, int* __restrict__ ids,
+                                 float* __restrict__ weights) {
   pdl_launch_dependents();
   pdl_wait();
   __shared__ float z[MOE_MAX_EXPERTS];
@@ -39,6 +40,14 @@ __global__ void moe_route_kernel(const T* __restrict__ h, int width, const W* __
   }
   __syncthreads();
   if (warp == 0) {
+    // softmax scores: e^(z - max) over the sum of all experts' (the order of the scores is the logits')
+    float z_max = -INFINITY, z_sum = 0.f;
+    if (softmax) {
+      for (int e = lane; e < n_experts; e += 32) z_max = fmaxf(z_max, z[e]);
+      z_max = warp_max(z_max);
+      for (int e = lane; e < n_experts; e += 32) z_sum += expf(z[e] - z_max);
+      z_sum = warp_sum(z_sum);
+    }
     float total = 0.f;
     for (int k = 0; k < top; ++k) {
       // the largest logit left; among equal ones the lowest index
@@ -51,7 +60,7 @@ __global__ void moe_route_kernel(const T* __restrict__ h, int width, const W* __
         int oa = __shfl_xor_sync(0xffffffffu, arg, o);
         if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
       }
-      float s = 1.0f / (1.0f + expf(-best));
+      float s = softmax ? expf(best - z_max) / z_sum : 1.0f / (1.0f + expf(-best));
       total += s;
       if (lane == 0) {
         ids[(size_t)t * top + k] = arg;
@@ -60,12 +69,20 @@ __global__ void moe_route_kernel(const T* __restrict__ h, int width, const W* __
       }
       __syncwarp();
     }
-    if (renormalise && lane < top) weights[(size_t)t * top + lane] /= total;
+    __syncwarp();
+    if (lane < top && (renormalise || weight_scale != 1.0f)) {
+      float wt = weights[(size_t)t * top + lane];
+      if (renormalise) wt /= total + sum_eps;
+      weights[(size_t)t * top + lane] = wt * weight_scale;
+    }
   }
 }
 
-extern "C" int bn_moe_route(const void* h, int h_dtype, int n_tokens, int width, const void* w, int w_dtype,
-                            int n_experts, int top, int renormalise, int* ids, float* weights, cudaStream_t stream) {
+// softmax: the scores are the softmax over all experts instead of each logit's logistic function; the chosen
+// experts' scores are divided by their sum + sum_eps with `renormalise`, then multiplied by weight_scale
+extern "C" int bn_moe_route_ex(const void* h, int h_dtype, int n_tokens, int width, const void* w, int w_dtype,
+                               int n_experts, int top, int renormalise, int softmax, float weight_scale, float sum_eps,
+                               int* ids, float* weights, cudaStream_t stream) {
   if (n_tokens <= 0) return BN_OK;
   if (!h || !w || !ids || !weights || width <= 0 || n_experts <= 0 || n_experts > MOE_MAX_EXPERTS || top <= 0 ||
       top > n_experts || top > 32 || (size_t)width * sizeof(float) > 40 * 1024)
@@ -73,17 +90,22 @@ extern "C" int bn_moe_route(const void* h, int h_dtype, int n_tokens, int width,
   const size_t smem = (size_t)width * sizeof(float);
   if (h_dtype == BN_F32 && w_dtype == BN_F32)
     BN_LAUNCH((moe_route_kernel<float, float>), n_tokens, 256, smem, stream, (const float*)h, width, (const float*)w,
-              n_experts, top, renormalise, ids, weights);
+              n_experts, top, renormalise, softmax, weight_scale, sum_eps, ids, weights);
   else if (h_dtype == BN_BF16 && w_dtype == BN_BF16)
     BN_LAUNCH((moe_route_kernel<__nv_bfloat16, __nv_bfloat16>), n_tokens, 256, smem, stream, (const __nv_bfloat16*)h, width,
-              (const __nv_bfloat16*)w, n_experts, top, renormalise, ids, weights);
+              (const __nv_bfloat16*)w, n_experts, top, renormalise, softmax, weight_scale, sum_eps, ids, weights);
   else if (h_dtype == BN_BF16 && w_dtype == BN_F32)
     BN_LAUNCH((moe_route_kernel<__nv_bfloat16, float>), n_tokens, 256, smem, stream, (const __nv_bfloat16*)h, width,
-              (const float*)w, n_experts, top, renormalise, ids, weights);
+              (const float*)w, n_experts, top, renormalise, softmax, weight_scale, sum_eps, ids, weights);
   else
     return BN_ERR_BAD_ARG;
   BN_CHECK_LAUNCH();
   return BN_OK;
+}
+
+extern "C" int bn_moe_route(const void* h, int h_dtype, int n_tokens, int width, const void* w, int w_dtype,
+                            int n_experts, int top, int renormalise, int* ids, float* weights, cudaStream_t stream) {
+  return bn_moe_route_ex(h, h_dtype, n_tokens, width, w, w_dtype, n_experts, top, renormalise, 0, 1.0f, 0.0f, ids, weights, stream);
 }
 
 #define MOE_THREADS 256
@@ -96,7 +118,7 @@ template <typename T>
 __global__ void moe_gate_up_kernel(const T* __restrict__ h, int width, const int* __restrict__ ids,
                                    const float* __restrict__ weights, int scale_input, const T* __restrict__ w_gate,
                                    const T* __restrict__ w_up, size_t expert_stride, int ff, int top, float limit,
-                                   float slope, T* __restrict__ y) {
+                                   float slope, int act, T* __restrict__ y) {
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ __align__(16) float xs[];  // width
@@ -127,9 +149,15 @@ __global__ void moe_gate_up_kernel(const T* __restrict__ h, int width, const int
       // the products' results pass through the compute type, as they do on the sorted path
       float g = lane == 0 ? g4[0] : lane == 1 ? g4[1] : lane == 2 ? g4[2] : g4[3];
       float u = lane == 0 ? u4[0] : lane == 1 ? u4[1] : lane == 2 ? u4[2] : u4[3];
-      g = fminf(to_f32<T>(from_f32<T>(g)), limit);
-      u = fminf(fmaxf(to_f32<T>(from_f32<T>(u)), -limit), limit);
-      y[(size_t)item * ff + j + lane] = from_f32<T>(g / (1.0f + expf(-slope * g)) * (u + 1.0f));
+      g = to_f32<T>(from_f32<T>(g));
+      u = to_f32<T>(from_f32<T>(u));
+      if (act >= 0) {  // the plain gated unit: act(g) * u
+        y[(size_t)item * ff + j + lane] = from_f32<T>(glu_activation(g, act) * u);
+      } else {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+        y[(size_t)item * ff + j + lane] = from_f32<T>(g / (1.0f + expf(-slope * g)) * (u + 1.0f));
+      }
     }
   }
 }
@@ -170,9 +198,10 @@ __global__ void moe_down_kernel(const T* __restrict__ y, int ff, const int* __re
   }
 }
 
-extern "C" int bn_moe_gate_up(const void* h, int dtype, int n_tokens, int width, const int* ids, const float* weights,
-                              int scale_input, const void* w_gate, const void* w_up, long long expert_stride, int ff, int top,
-                              float limit, float slope, void* y, cudaStream_t stream) {
+// act < 0: the clamped unit with `limit` and `slope`; act >= 0 (BN_ACT_*): act(gate) * up without clamps
+extern "C" int bn_moe_gate_up_ex(const void* h, int dtype, int n_tokens, int width, const int* ids, const float* weights,
+                                 int scale_input, const void* w_gate, const void* w_up, long long expert_stride, int ff, int top,
+                                 float limit, float slope, int act, void* y, cudaStream_t stream) {
   if (n_tokens <= 0) return BN_OK;
   if (!h || !ids || !weights || !w_gate || !w_up || !y || width <= 0 || ff <= 0 || top <= 0) return BN_ERR_BAD_ARG;
   size_t smem = (size_t)width * sizeof(float);
@@ -180,15 +209,22 @@ extern "C" int bn_moe_gate_up(const void* h, int dtype, int n_tokens, int width,
   dim3 grid(n_tokens * top, (ff + MOE_ROWS_PER_BLOCK - 1) / MOE_ROWS_PER_BLOCK);
   if (dtype == BN_F32)
     BN_LAUNCH(moe_gate_up_kernel<float>, grid, MOE_THREADS, smem, stream, (const float*)h, width, ids, weights, scale_input,
-              (const float*)w_gate, (const float*)w_up, (size_t)expert_stride, ff, top, limit, slope, (float*)y);
+              (const float*)w_gate, (const float*)w_up, (size_t)expert_stride, ff, top, limit, slope, act, (float*)y);
   else if (dtype == BN_BF16)
     BN_LAUNCH(moe_gate_up_kernel<__nv_bfloat16>, grid, MOE_THREADS, smem, stream, (const __nv_bfloat16*)h, width, ids,
               weights, scale_input, (const __nv_bfloat16*)w_gate, (const __nv_bfloat16*)w_up, (size_t)expert_stride, ff, top, limit,
-              slope, (__nv_bfloat16*)y);
+              slope, act, (__nv_bfloat16*)y);
   else
     return BN_ERR_BAD_ARG;
   BN_CHECK_LAUNCH();
   return BN_OK;
+}
+
+extern "C" int bn_moe_gate_up(const void* h, int dtype, int n_tokens, int width, const int* ids, const float* weights,
+                              int scale_input, const void* w_gate, const void* w_up, long long expert_stride, int ff, int top,
+                              float limit, float slope, void* y, cudaStream_t stream) {
+  return bn_moe_gate_up_ex(h, dtype, n_tokens, width, ids, weights, scale_input, w_gate, w_up, expert_stride, ff, top, limit, slope,
+                           -1, y, stream);
 }
 
 extern "C" int bn_moe_down(const void* y, int dtype, int n_tokens, int ff, const int* ids, const float* weights,

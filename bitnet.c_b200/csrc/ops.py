@@ -241,6 +241,19 @@ def glu_limited(h: torch.Tensor, out: torch.Tensor, limit: float, slope: float) 
     return out
 
 
+def glu_halves(h: torch.Tensor, out: torch.Tensor, act: int = 0) -> torch.Tensor:
+    """Rows of h hold ``inter`` gate values and then ``inter`` up values: out = act(gate) * up
+    (ACT_SILU, ACT_GELU_TANH)."""
+    _need(h, "h", dims=2)
+    _need(out, "out", h.dtype, 2)
+    inter = h.shape[1] // 2
+    if h.shape[1] != 2 * inter or tuple(out.shape) != (h.shape[0], inter):
+        raise KernelError(f"glu_halves: h {tuple(h.shape)} and out {tuple(out.shape)} do not fit")
+    _check(_fn("act", "bn_glu_halves")(_ptr(h), _ptr(out), int(_code(h)), int(h.shape[0]), int(inter), int(act), _stream()),
+           "glu_halves")
+    return out
+
+
 def scale_softcap(x: torch.Tensor, scale: float, softcap: float) -> torch.Tensor:
     """In place on float32 x: x * scale, then softcap * tanh(x / softcap) when softcap is not 0."""
     _need(x, "x", torch.float32)
@@ -313,7 +326,114 @@ def unit_norm_append(x: torch.Tensor, n_q_heads: int, head_dim: int, eps: float,
            "unit_norm_append")
 
 
+def slice_norm_append(x: torch.Tensor, q_len: int, wq: torch.Tensor, k_off: int, wk: torch.Tensor, v_off: int,
+                      n_kv_heads: int, head_dim: int, v_dim: int, eps: float, *, v_other: Optional[torch.Tensor] = None,
+                      blend: float = 0.0, tok_seq: Optional[torch.Tensor] = None, tok_pos: Optional[torch.Tensor] = None,
+                      slots: Optional[torch.Tensor] = None, page_table: Optional[torch.Tensor] = None,
+                      k_cache: Optional[torch.Tensor] = None, v_cache: Optional[torch.Tensor] = None) -> None:
+    """RMS norms with gains over the first ``q_len`` numbers of every row of x (all query heads at once) and over
+    the ``n_kv_heads * head_dim`` numbers at ``k_off`` (all key heads), in place; the values at ``v_off`` become
+    (1 - blend) v + blend v_other when ``v_other`` (a view with unit inner stride, one row per row of x) is given;
+    with a cache, the keys and values are then written into it."""
+    _need(x, "x", dims=2)
+    _need(wq, "wq", dims=1)
+    _need(wk, "wk", wq.dtype, 1)
+    k_len, v_len = n_kv_heads * head_dim, n_kv_heads * v_dim
+    n = x.shape[0]
+    if wq.shape[0] != q_len or wk.shape[0] != k_len or max(q_len, k_off + k_len, v_off + v_len) > x.shape[1]:
+        raise KernelError("slice_norm_append: slices or gains do not fit the rows")
+    other_stride = 0
+    if v_other is not None:
+        if (not v_other.is_cuda or v_other.dtype != x.dtype or v_other.dim() != 2 or v_other.stride(1) != 1
+                or v_other.shape[0] < n or v_other.shape[1] < v_len):
+            raise KernelError("slice_norm_append: v_other must be a CUDA view of x's type with unit inner stride that holds the values")
+        other_stride = v_other.stride(0)
+    pt_stride = 0
+    if k_cache is not None:
+        for t, nm in ((tok_seq, "tok_seq"), (tok_pos, "tok_pos"), (slots, "slots")):
+            _need(t, nm, torch.int32, 1)
+        _need(page_table, "page_table", torch.int32, 2)
+        _need(k_cache, "k_cache", x.dtype, 4)
+        _need(v_cache, "v_cache", x.dtype, 4)
+        if tuple(k_cache.shape[1:]) != (n_kv_heads, PAGE, head_dim) or tuple(v_cache.shape) != tuple(k_cache.shape[:3]) + (v_dim,):
+            raise KernelError(f"slice_norm_append: cache {tuple(k_cache.shape)} / {tuple(v_cache.shape)} does not fit")
+        if tok_pos.shape[0] != n:
+            raise KernelError("slice_norm_append: one position per row")
+        pt_stride = page_table.shape[1]
+    _check(_fn("unit_norm", "bn_slice_norm_append")(
+        _ptr(x), int(_code(x)), int(n), int(x.shape[1]), 0, int(q_len), _ptr(wq), int(k_off), int(k_len), _ptr(wk),
+        int(_code(wq)), c_float(eps), int(v_off), c_void_p(v_other.data_ptr()) if v_other is not None else _NULL,
+        int(other_stride), c_float(blend), int(n_kv_heads), int(head_dim), int(v_dim), _ptr(tok_seq), _ptr(tok_pos), _ptr(slots),
+        _ptr(page_table), int(pt_stride), _ptr(k_cache), _ptr(v_cache), _stream()), "slice_norm_append")
+
+
 # ---- attention ----------------------------------------------------------------------------
+def sigmoid_attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, n_tokens: int, n_heads: int, n_kv_heads: int,
+                      head_dim: int, scale: float, window: int, tok_seq: torch.Tensor, tok_pos: torch.Tensor,
+                      slots: torch.Tensor, page_table: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, *,
+                      rel: Optional[torch.Tensor] = None, mix: Optional[torch.Tensor] = None,
+                      gate: Optional[torch.Tensor] = None, gate_stride: int = 0, gate_per_head: bool = False,
+                      max_keys: int = 0) -> torch.Tensor:
+    """Causal attention without a softmax of every new token over its sequence's pages: a key at distance
+    n < window (window 0: every earlier key) weighs sigmoid(q . k * scale + rel[min(n, last)][head]); with ``mix``
+    ``[heads, heads]`` float32 the heads' weights are mixed, weight_h <- sum_g mix[h, g] weight_g; head h sums
+    the values of its own key/value head; ``gate`` (a view with unit inner stride, row stride ``gate_stride``)
+    holds one number per output number (or per head) whose logistic function multiplies the result.  q may be a
+    view into a wider row; a value head has the width of ``v_cache``'s rows.  ``max_keys``: a bound on the keys
+    any token sees; with few tokens the keys of a token are dealt out over several blocks."""
+    if not q.is_cuda or q.stride(-1) != 1:
+        raise KernelError("sigmoid_attention: q must be a CUDA tensor with unit inner stride")
+    _need(out, "out", q.dtype, 2)
+    for t, nm in ((tok_seq, "tok_seq"), (tok_pos, "tok_pos"), (slots, "slots")):
+        _need(t, nm, torch.int32, 1)
+    _need(page_table, "page_table", torch.int32, 2)
+    _need(k_cache, "k_cache", q.dtype, 4)
+    _need(v_cache, "v_cache", q.dtype, 4)
+    v_dim = v_cache.shape[3]
+    if tuple(k_cache.shape[1:]) != (n_kv_heads, PAGE, head_dim) or tuple(k_cache.shape[:3]) != tuple(v_cache.shape[:3]):
+        raise KernelError(f"sigmoid_attention: cache {tuple(k_cache.shape)} / {tuple(v_cache.shape)} is not "
+                          f"[pages, {n_kv_heads}, {PAGE}, {head_dim} / value width]")
+    if n_heads % n_kv_heads:
+        raise KernelError(f"sigmoid_attention: {n_heads} heads are not a multiple of {n_kv_heads} key/value heads")
+    if out.shape[0] < n_tokens or out.shape[1] != n_heads * v_dim:
+        raise KernelError("sigmoid_attention: out does not fit")
+    n_rel = 0
+    if rel is not None:
+        _need(rel, "rel", torch.float32, 2)
+        if rel.shape[1] != n_heads or rel.shape[0] < 1:
+            raise KernelError(f"sigmoid_attention: bias table {tuple(rel.shape)} is not [distances, {n_heads}]")
+        n_rel = rel.shape[0]
+    if mix is not None:
+        _need(mix, "mix", torch.float32, 2)
+        if tuple(mix.shape) != (n_heads, n_heads):
+            raise KernelError(f"sigmoid_attention: the mixing matrix {tuple(mix.shape)} is not [{n_heads}, {n_heads}]")
+    gate_mode = 0
+    if gate is not None:
+        gate_mode = 1 if gate_per_head else 2
+        need = n_heads if gate_per_head else n_heads * v_dim
+        if not gate.is_cuda or gate.dtype != q.dtype or gate.stride(-1) != 1 or gate.shape[-1] < need or gate_stride <= 0:
+            raise KernelError("sigmoid_attention: gate must be a CUDA view of q's type with unit inner stride that holds the gates")
+    smem_of = getattr(build.library("sigmoid_attention"), "bn_sigmoid_attention_smem")
+    smem_of.restype = c_int
+    if smem_of(int(_code(q)), int(n_heads), int(n_kv_heads), int(head_dim), int(v_dim), int(mix is not None)) > 200 * 1024:
+        raise KernelError(f"sigmoid_attention: {n_heads} heads of {head_dim} / {v_dim} numbers do not fit a block's shared memory")
+    splits = 1
+    if max_keys > DECODE_CHUNK and n_tokens < 2 * n_sms(q.device):
+        splits = min((max_keys + DECODE_CHUNK - 1) // DECODE_CHUNK, max(1, 4 * n_sms(q.device) // n_tokens))
+    part = None
+    if splits > 1:
+        part = torch.empty(n_tokens * splits * n_heads * v_dim, dtype=torch.float32, device=q.device)
+        global LAUNCHES
+        LAUNCHES += 1  # the kernel that adds the splits up
+    _check(_fn("sigmoid_attention", "bn_sigmoid_attention")(
+        _ptr(q), int(q_stride), _ptr(out), int(out.shape[1]), int(_code(q)), int(n_tokens), int(n_heads), int(n_kv_heads),
+        int(head_dim), int(v_dim), c_float(scale), int(window), _ptr(rel), int(n_rel), _ptr(mix),
+        c_void_p(gate.data_ptr()) if gate is not None else _NULL, int(gate_stride), int(gate_mode), _ptr(tok_seq), _ptr(tok_pos),
+        _ptr(slots), _ptr(page_table), int(page_table.shape[1]), _ptr(k_cache), _ptr(v_cache), _ptr(part), int(splits),
+        _stream()), "sigmoid_attention")
+    return out
+
+
 def attention_general(q: torch.Tensor, q_stride: int, out: torch.Tensor, n_tokens: int, n_heads: int,
                       n_kv_heads: int, head_dim: int, scale: float, window: int, tok_seq: torch.Tensor,
                       tok_pos: torch.Tensor, slots: torch.Tensor, page_table: torch.Tensor,
@@ -1307,9 +1427,11 @@ def delta_output(o: torch.Tensor, gain: torch.Tensor, gate: torch.Tensor, heads:
 
 
 # ---- mixture of experts -----------------------------------------------------------------------
-def moe_route(h: torch.Tensor, w_router: torch.Tensor, top: int, renormalise: bool = False):
-    """Per token the ``top`` experts with the largest router logits (float32 products), and the logistic
-    function of those logits as weights (divided by their sum with ``renormalise``):
+def moe_route(h: torch.Tensor, w_router: torch.Tensor, top: int, renormalise: bool = False, softmax: bool = False,
+              weight_scale: float = 1.0, sum_eps: float = 0.0):
+    """Per token the ``top`` experts with the largest router logits (float32 products), and their scores as
+    weights: the logistic function of each logit, or with ``softmax`` the softmax over all experts; divided by
+    the chosen ones' sum (+ ``sum_eps``) with ``renormalise``, then times ``weight_scale``:
     ``(ids int32 [T, top], weights float32 [T, top])``."""
     _need(h, "h", dims=2)
     _need(w_router, "w_router", dims=2)
@@ -1317,17 +1439,19 @@ def moe_route(h: torch.Tensor, w_router: torch.Tensor, top: int, renormalise: bo
         raise KernelError(f"moe_route: router {tuple(w_router.shape)}, top {top} do not fit rows of width {h.shape[1]}")
     ids = torch.empty((h.shape[0], top), dtype=torch.int32, device=h.device)
     weights = torch.empty((h.shape[0], top), dtype=torch.float32, device=h.device)
-    _check(_fn("moe", "bn_moe_route")(_ptr(h), int(_code(h)), int(h.shape[0]), int(h.shape[1]), _ptr(w_router),
-                                      int(_code(w_router)), int(w_router.shape[0]), int(top), int(bool(renormalise)),
-                                      _ptr(ids), _ptr(weights), _stream()), "moe_route")
+    _check(_fn("moe", "bn_moe_route_ex")(_ptr(h), int(_code(h)), int(h.shape[0]), int(h.shape[1]), _ptr(w_router),
+                                         int(_code(w_router)), int(w_router.shape[0]), int(top), int(bool(renormalise)),
+                                         int(bool(softmax)), c_float(weight_scale), c_float(sum_eps), _ptr(ids), _ptr(weights),
+                                         _stream()), "moe_route")
     return ids, weights
 
 
 def moe_experts_few(h: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gate_up: torch.Tensor,
                     w_down: torch.Tensor, limit: float, slope: float, scale_input: bool,
-                    add: Optional[torch.Tensor] = None) -> torch.Tensor:
+                    add: Optional[torch.Tensor] = None, act: int = -1) -> torch.Tensor:
     """The chosen experts of every token, streamed once per (token, expert): float32 ``[T, width]``, the sum over
     a token's experts plus ``add``.  The weight multiplies the expert's input (``scale_input``) or its output.
+    ``act`` < 0: the clamped unit with ``limit`` and ``slope``; ACT_SILU / ACT_GELU_TANH: act(gate) * up.
     ``w_gate_up`` ``[experts, 2 * ff, width]`` holds an expert's gate rows and then its up rows, ``w_down``
     ``[experts, width, ff]``; both in h's type."""
     _need(h, "h", dims=2)
@@ -1347,10 +1471,10 @@ def moe_experts_few(h: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w
             raise KernelError("moe_experts_few: add does not fit")
     y = torch.empty((T * top, ff), dtype=h.dtype, device=h.device)
     w_up = w_gate_up[:, ff:]
-    _check(_fn("moe", "bn_moe_gate_up")(_ptr(h), int(_code(h)), int(T), int(width), _ptr(ids), _ptr(weights),
-                                        int(bool(scale_input)), _ptr(w_gate_up), c_void_p(w_up.data_ptr()),
-                                        ctypes.c_longlong(2 * ff * width), int(ff), int(top), c_float(limit),
-                                        c_float(slope), _ptr(y), _stream()), "moe_gate_up")
+    _check(_fn("moe", "bn_moe_gate_up_ex")(_ptr(h), int(_code(h)), int(T), int(width), _ptr(ids), _ptr(weights),
+                                           int(bool(scale_input)), _ptr(w_gate_up), c_void_p(w_up.data_ptr()),
+                                           ctypes.c_longlong(2 * ff * width), int(ff), int(top), c_float(limit),
+                                           c_float(slope), int(act), _ptr(y), _stream()), "moe_gate_up")
     out = torch.empty((T, width), dtype=torch.float32, device=h.device)
     _check(_fn("moe", "bn_moe_down")(_ptr(y), int(_code(y)), int(T), int(ff), _ptr(ids), _ptr(weights),
                                      int(not scale_input), _ptr(w_down), int(width), int(top), _ptr(add),

@@ -120,7 +120,8 @@ class ParallelBlock(Block):
     """x <- x + (mixer(h) + ffn(h)) with h = norm(x): one norm, both sublayers read its output, and their deltas
     are summed before they meet the float32 stream.  Then, if the block has a ``side`` part, its input by token
     id: x <- x + norm'(side(x)).  The norm of whoever reads the stream next is taken in the same pass as the
-    last addition when that reader says which it is (``next_norm``)."""
+    last addition when that reader says which it is (``next_norm``).  With a second norm (``ffn_norm``) the
+    feed-forward reads that norm of the same x instead: x <- x + (mixer(norm(x)) + ffn(ffn_norm(x)))."""
 
     graph_safe = True  # as far as its parts are
     accepts_normed = True
@@ -131,9 +132,13 @@ class ParallelBlock(Block):
         self.mixer = build_part("mixer", spec.mixer, build)
         self.ffn = build_part("ffn", spec.ffn, build) if spec.ffn is not None else None
         self.side = build_part("side", spec.side, build) if spec.side is not None else None
+        ffn_norm = getattr(spec, "ffn_norm", None)
+        self.ffn_norm = build_part("norm", ffn_norm, build) if ffn_norm is not None else None
 
     def children(self):
         c = {"norm": self.norm, "mixer": self.mixer}
+        if self.ffn_norm is not None:
+            c["ffn_norm"] = self.ffn_norm
         if self.ffn is not None:
             c["ffn"] = self.ffn
         if self.side is not None:
@@ -155,9 +160,13 @@ class ParallelBlock(Block):
         else:
             h = self.norm.add_norm(x, pending, ctx)
         ctx.tap("attn_norm", h)
+        h2 = h
+        if self.ffn is not None and self.ffn_norm is not None:
+            h2 = self.ffn_norm.add_norm(x, None, ctx)  # the second norm of the same rows (the delta is in them by now)
+            ctx.tap("ffn_norm", h2)
         d = self.mixer.forward(h, ctx, kv, state)
         ctx.tap("attn_proj", d)
-        f = self.ffn.forward(h, ctx) if self.ffn is not None else None
+        f = self.ffn.forward(h2, ctx) if self.ffn is not None else None
         if f is not None:
             ctx.tap("ffn_out", f)
         if self.side is None:

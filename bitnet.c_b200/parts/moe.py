@@ -1,4 +1,4 @@
-"""Mixture of experts with logistic router scores and clamped gated experts."""
+"""Mixture of gated experts: logistic or softmax router scores, clamped or plain gated units."""
 from __future__ import annotations
 
 from typing import Dict
@@ -16,7 +16,10 @@ class Moe(FeedForward):
     s = sigmoid(z) and weights them by s; the weight multiplies the expert's input
     (``weight_on_input``) or its output.  An expert is down(g * sigmoid(slope g) * (u + 1)) with
     g = min(gate x, limit), u = clamp(up x, -limit, limit); a shared expert of the same form (sizes and
-    limit of its own) runs for every token and is added.
+    limit of its own) runs for every token and is added.  By the spec: ``scores`` "softmax" takes the softmax
+    over all experts as scores; ``renormalise`` divides the chosen ones' by their sum (+ ``renormalise_eps``);
+    ``weight_scale`` multiplies the weights; ``activation`` "silu" / "gelu_tanh" makes an expert
+    down(act(gate x) * (up x)) without clamps.
 
     Few rows (a decode step): two kernels stream the chosen experts once per (token, expert), from
     device memory alone.  Many rows: the (token, expert) items are sorted by expert and every expert's
@@ -26,6 +29,21 @@ class Moe(FeedForward):
     graph_safe = True  # the steps that are recorded are decode steps, which take the path without the host
     FEW_ITEMS = 64  # up to so many (token, expert) items the streaming kernels run
     PAD_FACTOR = 2.0  # blocks of equal size for all experts while they hold at most so many times the rows used
+
+    def __init__(self, spec, build):
+        super().__init__(spec, build)
+        scores, activation = getattr(spec, "scores", "sigmoid"), getattr(spec, "activation", "limited")
+        if scores not in ("sigmoid", "softmax"):
+            raise ValueError(f"router scores are 'sigmoid' or 'softmax', not {scores!r}")
+        if activation != "limited" and activation not in ops.ACTIVATIONS:
+            raise ValueError(f"expert activation {activation!r} is not built; known: limited, {', '.join(sorted(ops.ACTIVATIONS))}")
+        self.softmax = scores == "softmax"
+        self.act = -1 if activation == "limited" else ops.ACTIVATIONS[activation]  # -1: the clamped unit
+
+    def _activate(self, gate_up, out, limit):
+        if self.act < 0:
+            return ops.glu_limited(gate_up, out, limit, self.spec.slope)
+        return ops.glu_halves(gate_up, out, self.act)
 
     def params(self) -> Dict[str, ParamSpec]:
         s = self.spec
@@ -55,19 +73,20 @@ class Moe(FeedForward):
     def _expert(self, x, w_gate_up, w_down, limit, out_dtype):
         gu = ops.linear(x, w_gate_up, out_dtype=self.build.dtype)
         act = torch.empty((x.shape[0], gu.shape[1] // 2), dtype=gu.dtype, device=gu.device)
-        ops.glu_limited(gu, act, limit, self.spec.slope)
+        self._activate(gu, act, limit)
         return ops.linear(act, w_down, out_dtype=out_dtype)
 
     def forward(self, h, ctx):
         s = self.spec
         T = h.shape[0]
         shared = self._expert(h, self.w_shared_gate_up, self.w_shared_down, s.shared_limit, torch.float32) if s.shared_ff else None
-        ids, weights = ops.moe_route(h, self.w_router, s.top, s.renormalise)
+        ids, weights = ops.moe_route(h, self.w_router, s.top, s.renormalise, softmax=self.softmax,
+                                     weight_scale=getattr(s, "weight_scale", 1.0), sum_eps=getattr(s, "renormalise_eps", 0.0))
         if ctx.diag is not None:
             ctx.tap("moe_ids", lambda: ids.float())
         if ctx.decode or T * s.top <= self.FEW_ITEMS:
             return ops.moe_experts_few(h, ids, weights, self.w_gate_up, self.w_down, s.expert_limit, s.slope,
-                                       s.weight_on_input, add=shared)
+                                       s.weight_on_input, add=shared, act=self.act)
         counts = ops.moe_count(ids, s.n_experts)
         per_expert = counts.cpu().tolist()  # the one place where the host waits for the device
         dt, dev_ = self.build.dtype, h.device
@@ -78,7 +97,7 @@ class Moe(FeedForward):
             x_pad, place, _ = ops.moe_sort(h, ids, weights, counts, s.weight_on_input, cap=cap)
             gate_up = ops.batched_matmul(x_pad.view(s.n_experts, cap, s.width), self.w_gate_up)
             act = torch.empty((s.n_experts * cap, s.expert_ff), dtype=dt, device=dev_)
-            ops.glu_limited(gate_up.view(s.n_experts * cap, 2 * s.expert_ff), act, s.expert_limit, s.slope)
+            self._activate(gate_up.view(s.n_experts * cap, 2 * s.expert_ff), act, s.expert_limit)
             y_pad = ops.batched_matmul(act.view(s.n_experts, cap, s.expert_ff), self.w_down)
             return ops.moe_gather(y_pad.view(s.n_experts * cap, s.width), place, weights, not s.weight_on_input, add=shared)
         # uneven: the experts' rows packed side by side, their products one after another into slices
@@ -91,7 +110,7 @@ class Moe(FeedForward):
             if at[e + 1] > at[e]:
                 ops.matmul_into(x_sorted[at[e]: at[e + 1]], self.w_gate_up[e], gate_up[at[e]: at[e + 1]])
         act = torch.empty((T * s.top, s.expert_ff), dtype=dt, device=dev_)
-        ops.glu_limited(gate_up, act, s.expert_limit, s.slope)
+        self._activate(gate_up, act, s.expert_limit)
         y_sorted = torch.empty((T * s.top, s.width), dtype=dt, device=dev_)
         for e in range(s.n_experts):
             if at[e + 1] > at[e]:
