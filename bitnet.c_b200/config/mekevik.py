@@ -100,14 +100,14 @@ class MekevikConfig:
             raise ConfigError(f"config.json: {where}.bias_max={bias_max} must exceed half the {buckets} distance buckets")
         value_mix = "none"
         if m.get("v_mix"):
-            # the first layer that blends is the source of the others, which must have values of the same shape
+            # the first layer that blends is the source of the others, whose tokens must have as many value numbers
             if not source:
-                source.update(layer=i, shape=(kv_heads, vdim))
+                source.update(layer=i, size=kv_heads * vdim)
                 value_mix = "source"
             else:
-                if source["shape"] != (kv_heads, vdim):
-                    raise ConfigError(f"config.json: {where}.v_mix: kv_heads x vdim = {kv_heads} x {vdim}, but layer "
-                                      f"{source['layer']}, whose values it blends in, has {source['shape'][0]} x {source['shape'][1]}")
+                if source["size"] != kv_heads * vdim:
+                    raise ConfigError(f"config.json: {where}.v_mix: kv_heads x vdim = {kv_heads} x {vdim} = {kv_heads * vdim} numbers "
+                                      f"per token, but layer {source['layer']}, whose values it blends in, has {source['size']}")
                 value_mix = "blend"
         return SigmoidAttentionSpec(width=self.width, n_heads=heads, n_kv_heads=kv_heads, head_dim=dim, v_head_dim=vdim,
                                     scale=_num(m, "scale", where), window=window, whole_norm=True, norm_eps=eps,

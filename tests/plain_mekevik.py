@@ -24,6 +24,14 @@ def _id(a):
     return a
 
 
+def to_bf16(a):
+    """Round to the nearest bfloat16 (ties to even), returned as float64."""
+    f = np.ascontiguousarray(a, dtype=np.float32)
+    u = f.view(np.uint32).astype(np.uint64)
+    u = ((u + 0x7FFF + ((u >> 16) & 1)) >> 16) << 16
+    return u.astype(np.uint32).view(np.float32).astype(np.float64).reshape(np.shape(a))
+
+
 # ---- small pieces ------------------------------------------------------------------------------
 def rms_norm(x: np.ndarray, w: np.ndarray, eps: float) -> np.ndarray:
     """x / sqrt(mean(x^2) + eps) * w over the last axis."""
@@ -50,8 +58,9 @@ def distance_bucket(n: int, n_buckets: int, max_distance: int) -> int:
 
 
 def visible(i: int, j: int, window: int) -> bool:
-    """Whether the query at position i sees the key at position j: itself and the window - 1 before it."""
-    return 0 <= i - j < window
+    """Whether the query at position i sees the key at position j: itself and the window - 1 before it
+    (window 0: every earlier key)."""
+    return 0 <= i - j and (window <= 0 or i - j < window)
 
 
 def attention_queries_keys(h, w, p, m, eps, r=_id):
@@ -69,7 +78,7 @@ def attention_values(h, w, p, m, v_first, r=_id):
     v = r(h @ w[p + "v"].T).reshape(T, m["kv_heads"], m["vdim"])
     if v_first is not None:
         lam = float(w[p + "vmix"])
-        v = r((1.0 - lam) * v + lam * v_first)
+        v = r((1.0 - lam) * v + lam * v_first.reshape(v.shape))  # number by number over all heads
     return v
 
 
@@ -80,10 +89,11 @@ def attention_weights(q, k, w, p, m):
     G = k.shape[1]
     rel = w[p + "rel"]
     B = rel.shape[0]
-    window = int(m["mask"]["size"])
+    window = int((m.get("mask") or {}).get("size", 0))
     bucket_of = np.array([distance_bucket(n, B, m["bias_max"]) for n in range(T)])
     i, j = np.arange(T)[:, None], np.arange(T)[None, :]
-    seen = (i - j >= 0) & (i - j < window)
+    seen = np.array([[visible(a, b, window) for b in range(T)] for a in range(T)]) if T <= 48 else \
+        (i - j >= 0) & ((window <= 0) | (i - j < window))
     a = np.zeros((H, T, T))
     for hd in range(H):
         g = hd // (H // G)
