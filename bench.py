@@ -494,6 +494,32 @@ LOTILIX_SIZES = {
 }
 
 
+def mekevik_sizes(width, heads, kv_heads, dim, vdim, window, ff, experts, top, vocab):
+    """A Mekevik configuration of four layers (attention without a softmax in each, with mixed heads, blended
+    values and a window; the feed-forward dense, experts, dense, experts, where a token's experts are together as
+    wide as the dense unit) and the Llama configuration of the same width, heads, layers, vocabulary and
+    feed-forward width."""
+    att = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": dim ** -0.5 * 4, "bias_max": 4 * window,
+           "mask": {"size": window}, "v_mix": True}
+    dense = {"kind": "dense", "ff": ff, "limit": 7.0}
+    moe = {"kind": "moe", "router": {"experts": experts, "top": top, "scale": 1.0}, "expert": {"ff": ff // top}}
+    layers = [{"type": "attention", "mixer": dict(att), "mlp": mlp} for mlp in (dense, moe, dense, moe)]
+    mek = {"architecture": "Mekevik", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0},
+           "logit_scale": 1.0, "layers": layers, "max_positions": 8192}
+    llama = {"architectures": ["LlamaForCausalLM"], "model_type": "llama", "hidden_size": width, "intermediate_size": ff,
+             "num_hidden_layers": len(layers), "num_attention_heads": heads, "num_key_value_heads": kv_heads, "head_dim": dim,
+             "vocab_size": vocab, "max_position_embeddings": 8192, "rope_theta": 500000.0, "rms_norm_eps": 1e-5,
+             "tie_word_embeddings": False, "hidden_act": "silu"}
+    return mek, llama
+
+
+MEKEVIK_SIZES = {
+    "w1024": dict(width=1024, heads=8, kv_heads=2, dim=128, vdim=128, window=1024, ff=4096, experts=8, top=2, vocab=32000),
+    "w2048": dict(width=2048, heads=16, kv_heads=4, dim=128, vdim=128, window=1024, ff=8192, experts=8, top=2, vocab=32000),
+    "w4096": dict(width=4096, heads=32, kv_heads=8, dim=128, vdim=128, window=1024, ff=14336, experts=8, top=2, vocab=32000),
+}
+
+
 def kernel_classes(model, vocab, tokens, batch, prompt_len):
     """Device time by entry point (ms) of one step of ``tokens`` prompt tokens and of one decode step of
     ``batch`` sequences behind prompts of ``prompt_len``, each kernel between two events (no graph, so the
@@ -534,7 +560,7 @@ def kernel_classes(model, vocab, tokens, batch, prompt_len):
 
 
 def run_design(args):
-    """``--design fesorax | lotilix``: prefill and decode throughput of that design at layer sizes of real
+    """``--design fesorax | lotilix | mekevik``: prefill and decode throughput of that design at layer sizes of real
     models (random weights, bfloat16), beside the Llama decoder of equal width, heads, layers, vocabulary and
     feed-forward work per token, with each step's device time by kernel entry point."""
     import torch
@@ -543,7 +569,8 @@ def run_design(args):
     rec = {"metric": "prefill and decode tokens/s of the Fesorax design beside Llama at equal size", "impl": "ours",
            "dtype": "bf16", "data": "synthetic", "n_gpus": 1, "peaks": pk, "prefill_tokens": PREFILL_TOKENS,
            "decode_batch": args.batch, "decode_prompt": PROMPT_LEN, "sizes": {}}
-    sizes, maker = (LOTILIX_SIZES, lotilix_sizes) if args.design == "lotilix" else (DESIGN_SIZES, fesorax_sizes)
+    sizes, maker = {"lotilix": (LOTILIX_SIZES, lotilix_sizes), "mekevik": (MEKEVIK_SIZES, mekevik_sizes),
+                    "fesorax": (DESIGN_SIZES, fesorax_sizes)}[args.design]
     rec["metric"] = rec["metric"].replace("Fesorax", args.design.capitalize())
     names = [n for n in sizes if not args.sizes or n in args.sizes.split(",")]
     for name in names:
@@ -583,7 +610,7 @@ def main():
                          "(comparisons, profiling)")
     ap.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16",
                     help="compute type of the main decode run (float32: profiling of the 32-bit path, with --skip-points)")
-    ap.add_argument("--design", choices=["fesorax", "lotilix"],
+    ap.add_argument("--design", choices=["fesorax", "lotilix", "mekevik"],
                     help="measure another design of the library beside Llama at equal size instead (prefill, decode, "
                          "time by kernel); the default workload and its record stay as they are")
     ap.add_argument("--sizes", default="", help="with --design: which size sets, with commas (default: all)")

@@ -50,6 +50,7 @@ SOURCES: Dict[str, str] = {
     "rotary_pairs": "rotary_pairs.cu",
     "delta_rule": "delta_rule.cu",
     "sigmoid_attention": "sigmoid_attention.cu",
+    "sigmoid_attention_prefill": "sigmoid_attention_prefill.cu",
 }
 
 NVCC_FLAGS = [

@@ -198,6 +198,19 @@ __global__ void moe_down_kernel(const T* __restrict__ y, int ff, const int* __re
   }
 }
 
+// Shared memory beyond the default 48 KB is asked for once per kernel and size (up to MOE_SMEM_MAX bytes).
+#define MOE_SMEM_MAX (200 * 1024)
+template <typename K>
+static int moe_grant_smem(K kernel, size_t smem, size_t* granted) {
+  if (smem > MOE_SMEM_MAX) return BN_ERR_BAD_ARG;
+  if (smem > 48 * 1024 && smem > *granted) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return BN_ERR_LAUNCH + (int)e;
+    *granted = smem;
+  }
+  return BN_OK;
+}
+
 // act < 0: the clamped unit with `limit` and `slope`; act >= 0 (BN_ACT_*): act(gate) * up without clamps
 extern "C" int bn_moe_gate_up_ex(const void* h, int dtype, int n_tokens, int width, const int* ids, const float* weights,
                                  int scale_input, const void* w_gate, const void* w_up, long long expert_stride, int ff, int top,
@@ -205,7 +218,10 @@ extern "C" int bn_moe_gate_up_ex(const void* h, int dtype, int n_tokens, int wid
   if (n_tokens <= 0) return BN_OK;
   if (!h || !ids || !weights || !w_gate || !w_up || !y || width <= 0 || ff <= 0 || top <= 0) return BN_ERR_BAD_ARG;
   size_t smem = (size_t)width * sizeof(float);
-  if (smem > 48 * 1024) return BN_ERR_BAD_ARG;
+  static size_t granted[2] = {0, 0};
+  int rc = dtype == BN_F32 ? moe_grant_smem(moe_gate_up_kernel<float>, smem, &granted[0])
+                           : moe_grant_smem(moe_gate_up_kernel<__nv_bfloat16>, smem, &granted[1]);
+  if (rc != BN_OK) return rc;
   dim3 grid(n_tokens * top, (ff + MOE_ROWS_PER_BLOCK - 1) / MOE_ROWS_PER_BLOCK);
   if (dtype == BN_F32)
     BN_LAUNCH(moe_gate_up_kernel<float>, grid, MOE_THREADS, smem, stream, (const float*)h, width, ids, weights, scale_input,
@@ -234,7 +250,10 @@ extern "C" int bn_moe_down(const void* y, int dtype, int n_tokens, int ff, const
   if (!y || !ids || !weights || !w_down || !out || width <= 0 || ff <= 0 || top <= 0) return BN_ERR_BAD_ARG;
   dim3 grid(n_tokens, (width + MOE_ROWS_PER_BLOCK - 1) / MOE_ROWS_PER_BLOCK);
   const size_t smem = (size_t)top * ff * sizeof(float);
-  if (smem > 48 * 1024) return BN_ERR_BAD_ARG;
+  static size_t granted[2] = {0, 0};
+  int rc = dtype == BN_F32 ? moe_grant_smem(moe_down_kernel<float>, smem, &granted[0])
+                           : moe_grant_smem(moe_down_kernel<__nv_bfloat16>, smem, &granted[1]);
+  if (rc != BN_OK) return rc;
   if (dtype == BN_F32)
     BN_LAUNCH(moe_down_kernel<float>, grid, MOE_THREADS, smem, stream, (const float*)y, ff, ids, weights, scale_output,
               (const float*)w_down, width, top, add, add_dtype, out);

@@ -1427,6 +1427,60 @@ def delta_output(o: torch.Tensor, gain: torch.Tensor, gate: torch.Tensor, heads:
 
 
 # ---- mixture of experts -----------------------------------------------------------------------
+def sigmoid_attention_prefill_fits(n_heads: int, n_kv_heads: int, head_dim: int, v_dim: int) -> bool:
+    """Whether the tensor-core kernel for runs of new tokens takes these sizes (bfloat16 only)."""
+    fn = getattr(build.library("sigmoid_attention_prefill"), "bn_sigmoid_attention_prefill_fits")
+    fn.restype = c_int
+    return bool(fn(int(n_heads), int(n_kv_heads), int(head_dim), int(v_dim)))
+
+
+def sigmoid_attention_prefill(q: torch.Tensor, q_stride: int, out: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
+                              scale: float, window: int, tile_seq: torch.Tensor, tile_row0: torch.Tensor, seq_start: torch.Tensor,
+                              seq_pos0: torch.Tensor, slots: torch.Tensor, page_table: torch.Tensor, k_cache: torch.Tensor,
+                              v_cache: torch.Tensor, *, rel: Optional[torch.Tensor] = None, mix: Optional[torch.Tensor] = None,
+                              gate: Optional[torch.Tensor] = None, gate_stride: int = 0, gate_per_head: bool = False) -> torch.Tensor:
+    """``sigmoid_attention`` for runs of new tokens in bfloat16 on the tensor cores: block i of the step's list
+    handles up to 64 new tokens of sequence tile_seq[i] from its row tile_row0[i] on, 16 at a time, each by a
+    cluster of one thread block per key/value head.  The same arguments and the same result up to rounding."""
+    if not q.is_cuda or q.dtype != torch.bfloat16 or q.stride(-1) != 1:
+        raise KernelError("sigmoid_attention_prefill: q must be a bfloat16 CUDA tensor with unit inner stride")
+    _need(out, "out", q.dtype, 2)
+    for t, nm in ((tile_seq, "tile_seq"), (tile_row0, "tile_row0"), (seq_start, "seq_start"), (seq_pos0, "seq_pos0"), (slots, "slots")):
+        _need(t, nm, torch.int32, 1)
+    _need(page_table, "page_table", torch.int32, 2)
+    _need(k_cache, "k_cache", q.dtype, 4)
+    _need(v_cache, "v_cache", q.dtype, 4)
+    v_dim = v_cache.shape[3]
+    if tuple(k_cache.shape[1:]) != (n_kv_heads, PAGE, head_dim) or tuple(k_cache.shape[:3]) != tuple(v_cache.shape[:3]):
+        raise KernelError(f"sigmoid_attention_prefill: cache {tuple(k_cache.shape)} / {tuple(v_cache.shape)} is not "
+                          f"[pages, {n_kv_heads}, {PAGE}, {head_dim} / value width]")
+    if out.shape[1] != n_heads * v_dim or not sigmoid_attention_prefill_fits(n_heads, n_kv_heads, head_dim, v_dim):
+        raise KernelError("sigmoid_attention_prefill: sizes do not fit this kernel")
+    n_rel = 0
+    if rel is not None:
+        _need(rel, "rel", torch.float32, 2)
+        if rel.shape[1] != n_heads or rel.shape[0] < 1:
+            raise KernelError(f"sigmoid_attention_prefill: bias table {tuple(rel.shape)} is not [distances, {n_heads}]")
+        n_rel = rel.shape[0]
+    if mix is not None:
+        _need(mix, "mix", torch.float32, 2)
+        if tuple(mix.shape) != (n_heads, n_heads):
+            raise KernelError(f"sigmoid_attention_prefill: the mixing matrix {tuple(mix.shape)} is not [{n_heads}, {n_heads}]")
+    gate_mode = 0
+    if gate is not None:
+        gate_mode = 1 if gate_per_head else 2
+        need = n_heads if gate_per_head else n_heads * v_dim
+        if not gate.is_cuda or gate.dtype != q.dtype or gate.stride(-1) != 1 or gate.shape[-1] < need or gate_stride <= 0:
+            raise KernelError("sigmoid_attention_prefill: gate must be a CUDA view of q's type with unit inner stride that holds the gates")
+    _check(_fn("sigmoid_attention_prefill", "bn_sigmoid_attention_prefill")(
+        _ptr(q), int(q_stride), _ptr(out), int(out.shape[1]), int(tile_seq.shape[0]), int(n_heads), int(n_kv_heads), int(head_dim),
+        int(v_dim), c_float(scale), int(window), _ptr(rel), int(n_rel), _ptr(mix),
+        c_void_p(gate.data_ptr()) if gate is not None else _NULL, int(gate_stride), int(gate_mode), _ptr(tile_seq), _ptr(tile_row0),
+        _ptr(seq_start), _ptr(seq_pos0), _ptr(slots), _ptr(page_table), int(page_table.shape[1]), _ptr(k_cache), _ptr(v_cache),
+        _stream()), "sigmoid_attention_prefill")
+    return out
+
+
 def moe_route(h: torch.Tensor, w_router: torch.Tensor, top: int, renormalise: bool = False, softmax: bool = False,
               weight_scale: float = 1.0, sum_eps: float = 0.0):
     """Per token the ``top`` experts with the largest router logits (float32 products), and their scores as
@@ -1446,6 +1500,15 @@ def moe_route(h: torch.Tensor, w_router: torch.Tensor, top: int, renormalise: bo
     return ids, weights
 
 
+MOE_FEW_SMEM = 200 * 1024  # bytes of shared memory the streaming expert kernels may take (moe.cu: MOE_SMEM_MAX)
+
+
+def moe_few_fits(width: int, top: int, ff: int) -> bool:
+    """Whether the streaming expert kernels hold a token's input (``width`` float32) and its experts' activations
+    (``top * ff`` float32) in a block's shared memory."""
+    return 4 * width <= MOE_FEW_SMEM and 4 * top * ff <= MOE_FEW_SMEM
+
+
 def moe_experts_few(h: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gate_up: torch.Tensor,
                     w_down: torch.Tensor, limit: float, slope: float, scale_input: bool,
                     add: Optional[torch.Tensor] = None, act: int = -1) -> torch.Tensor:
@@ -1463,7 +1526,7 @@ def moe_experts_few(h: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w
     _need(w_down, "w_down", h.dtype, 3)
     E, ff = w_gate_up.shape[0], w_gate_up.shape[1] // 2
     if (tuple(w_gate_up.shape) != (E, 2 * ff, width) or tuple(w_down.shape) != (E, width, ff)
-            or tuple(ids.shape) != (T, top) or tuple(weights.shape) != (T, top) or width * 4 > 48 * 1024):
+            or tuple(ids.shape) != (T, top) or tuple(weights.shape) != (T, top) or not moe_few_fits(width, top, ff)):
         raise KernelError("moe_experts_few: sizes do not fit")
     if add is not None:
         _need(add, "add", dims=2)

@@ -39,6 +39,10 @@ class Moe(FeedForward):
             raise ValueError(f"expert activation {activation!r} is not built; known: limited, {', '.join(sorted(ops.ACTIVATIONS))}")
         self.softmax = scores == "softmax"
         self.act = -1 if activation == "limited" else ops.ACTIVATIONS[activation]  # -1: the clamped unit
+        # experts too wide for the streaming kernels' shared memory always take the sorted path, which asks the
+        # device for the experts' counts: such a model's steps are not recorded
+        self.few_fits = ops.moe_few_fits(spec.width, spec.top, spec.expert_ff)
+        self.graph_safe = self.few_fits
 
     def _activate(self, gate_up, out, limit):
         if self.act < 0:
@@ -84,7 +88,7 @@ class Moe(FeedForward):
                                      weight_scale=getattr(s, "weight_scale", 1.0), sum_eps=getattr(s, "renormalise_eps", 0.0))
         if ctx.diag is not None:
             ctx.tap("moe_ids", lambda: ids.float())
-        if ctx.decode or T * s.top <= self.FEW_ITEMS:
+        if self.few_fits and (ctx.decode or T * s.top <= self.FEW_ITEMS):
             return ops.moe_experts_few(h, ids, weights, self.w_gate_up, self.w_down, s.expert_limit, s.slope,
                                        s.weight_on_input, add=shared, act=self.act)
         counts = ops.moe_count(ids, s.n_experts)

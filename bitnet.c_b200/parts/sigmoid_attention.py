@@ -23,8 +23,9 @@ class SigmoidAttention(Mixer):
     The source layer of a value group leaves its values (a view into its stacked projections) in the step's
     ``memo``; the layers that blend run after it in the same step and read the rows of the same tokens."""
 
-    kernels = ("linear", "linear_mma", "linear_tc", "gemm_tc", "unit_norm", "sigmoid_attention")
+    kernels = ("linear", "linear_mma", "linear_tc", "gemm_tc", "unit_norm", "sigmoid_attention", "sigmoid_attention_prefill")
     graph_safe = True
+    TILED_MIN_TOKENS = 16  # a sequence brings at least so many new tokens: the tensor-core kernel runs
 
     def __init__(self, spec, build):
         super().__init__(spec, build)
@@ -105,6 +106,8 @@ class SigmoidAttention(Mixer):
         self.mix = tensors["talk"].float().contiguous() if s.head_mix else None
         if s.value_mix == "blend":
             self.blend = float(tensors["vmix"].float().item())
+        self.tiled_fits = (self.build.dtype == torch.bfloat16
+                           and ops.sigmoid_attention_prefill_fits(s.n_heads, s.n_kv_heads, s.head_dim, s.v_head_dim))
 
     def cache_request(self) -> KvRequest:
         s = self.spec
@@ -130,6 +133,13 @@ class SigmoidAttention(Mixer):
             ctx.tap("attn_q", lambda: proj[:, : self.q_dim])
         out = torch.empty((n, self.o_dim), dtype=self.build.dtype, device=h.device)
         gate = proj[:, self.g_off:] if s.output_gate else None
+        if (self.build.dtype == torch.bfloat16 and not ctx.decode and ctx.tile_seq is not None and ctx.max_new >= self.TILED_MIN_TOKENS
+                and self.tiled_fits):
+            ops.sigmoid_attention_prefill(proj, self.row, out, s.n_heads, s.n_kv_heads, s.head_dim, s.scale, s.window, ctx.tile_seq,
+                                          ctx.tile_row0, ctx.seq_start, ctx.seq_pos0, ctx.slots, kv.page_table, kv.k, kv.v,
+                                          rel=self.rel, mix=self.mix, gate=gate, gate_stride=self.row)
+            ctx.tap("attn_out", out)
+            return ops.linear(out, self.w_o, out_dtype=torch.float32)
         ops.sigmoid_attention(proj, self.row, out, n, s.n_heads, s.n_kv_heads, s.head_dim, s.scale, s.window, ctx.tok_seq,
                               ctx.tok_pos, ctx.slots, kv.page_table, kv.k, kv.v, rel=self.rel, mix=self.mix, gate=gate,
                               gate_stride=self.row, max_keys=min(ctx.max_len, s.window) if s.window > 0 else ctx.max_len)

@@ -104,7 +104,7 @@ class SafetensorsFile:
 
 
 def _raw_bytes(t: torch.Tensor) -> bytes:
-    t = t.detach().cpu().contiguous()
+    t = t.detach().cpu().contiguous().reshape(-1)  # flat: a tensor of shape () has bytes too
     return t.view(torch.uint8).numpy().tobytes() if t.numel() else b""
 
 

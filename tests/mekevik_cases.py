@@ -137,7 +137,7 @@ def write_folder(folder: str, cfg: dict, weights: dict, storage: str = "bfloat16
     os.makedirs(folder, exist_ok=True)
     dt = {"bfloat16": torch.bfloat16, "float32": torch.float32}[storage]
     write_safetensors(os.path.join(folder, "model.safetensors"),
-                      [(n, torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).to(dt)) for n, a in weights.items()])
+                      [(n, torch.tensor(np.asarray(a, dtype=np.float32)).to(dt)) for n, a in weights.items()])  # a blend's weight keeps its shape ()
     with open(os.path.join(folder, "config.json"), "w") as f:
         json.dump(cfg, f)
     return folder

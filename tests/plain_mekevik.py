@@ -143,6 +143,13 @@ def expert(h, w, p, r=_id):
     return r(r(silu(r(h @ w[p + "gate"].T)) * r(h @ w[p + "up"].T)) @ w[p + "down"].T)
 
 
+def router_margins(h, w, p, mlp):
+    """Per token how far the last chosen expert's logit lies above the first one left out (inf when all are chosen)."""
+    z = np.sort(h @ w[p + "router"].T, axis=-1)[:, ::-1]
+    top = mlp["router"]["top"]
+    return z[:, top - 1] - z[:, top] if top < z.shape[1] else np.full(h.shape[0], np.inf)
+
+
 def moe_ffn(h, w, p, mlp, r=_id):
     ids, weights = router(h, w, p, mlp)
     out = np.zeros((h.shape[0], w[p + "e0.down"].shape[0]))
@@ -153,8 +160,10 @@ def moe_ffn(h, w, p, mlp, r=_id):
 
 
 # ---- the model ---------------------------------------------------------------------------------
-def forward(cfg: Dict, w: Dict[str, np.ndarray], tokens: Sequence[int], round_fn=_id, layers_out: Optional[List] = None):
-    """Logits [T, vocab] of one sequence.  ``layers_out``: a list that receives the stream after every layer."""
+def forward(cfg: Dict, w: Dict[str, np.ndarray], tokens: Sequence[int], round_fn=_id, layers_out: Optional[List] = None,
+            margins_out: Optional[List] = None):
+    """Logits [T, vocab] of one sequence.  ``layers_out``: a list that receives the stream after every layer;
+    ``margins_out``: one that receives every router's margins per token."""
     r = round_fn
     eps = cfg["norm"]["eps"]
     x = w["embed"][np.asarray(tokens)] * cfg["embedding"]["scale"]
@@ -169,6 +178,8 @@ def forward(cfg: Dict, w: Dict[str, np.ndarray], tokens: Sequence[int], round_fn
             v_first = v
         if mlp is not None:
             h2 = r(rms_norm(x, w[p + "norm2"], eps))
+            if margins_out is not None and mlp["kind"] == "moe":
+                margins_out.append(router_margins(h2, w, p + "mlp.", mlp))
             d = d + (dense_ffn(h2, w, p + "mlp.", mlp, r) if mlp["kind"] == "dense" else moe_ffn(h2, w, p + "mlp.", mlp, r))
         x = x + d
         if layers_out is not None:
