@@ -1438,15 +1438,23 @@ def sigmoid_attention_prefill(q: torch.Tensor, q_stride: int, out: torch.Tensor,
                               scale: float, window: int, tile_seq: torch.Tensor, tile_row0: torch.Tensor, seq_start: torch.Tensor,
                               seq_pos0: torch.Tensor, slots: torch.Tensor, page_table: torch.Tensor, k_cache: torch.Tensor,
                               v_cache: torch.Tensor, *, rel: Optional[torch.Tensor] = None, mix: Optional[torch.Tensor] = None,
-                              gate: Optional[torch.Tensor] = None, gate_stride: int = 0, gate_per_head: bool = False) -> torch.Tensor:
+                              gate: Optional[torch.Tensor] = None, gate_stride: int = 0, gate_per_head: bool = False,
+                              splits: int = 1) -> torch.Tensor:
     """``sigmoid_attention`` for runs of new tokens in bfloat16 on the tensor cores: block i of the step's list
     handles up to 64 new tokens of sequence tile_seq[i] from its row tile_row0[i] on, 16 at a time, each by a
-    cluster of one thread block per key/value head.  The same arguments and the same result up to rounding."""
+    cluster of one thread block per key/value head.  The same arguments and the same result up to rounding.
+    ``splits`` > 1, for steps in which no listed block holds more than 16 rows (one token per sequence: then
+    ``tile_row0`` may be None): the pages a block of rows sees are dealt out over so many clusters, and a second
+    kernel adds their sums up."""
     if not q.is_cuda or q.dtype != torch.bfloat16 or q.stride(-1) != 1:
         raise KernelError("sigmoid_attention_prefill: q must be a bfloat16 CUDA tensor with unit inner stride")
     _need(out, "out", q.dtype, 2)
-    for t, nm in ((tile_seq, "tile_seq"), (tile_row0, "tile_row0"), (seq_start, "seq_start"), (seq_pos0, "seq_pos0"), (slots, "slots")):
+    for t, nm in ((tile_seq, "tile_seq"), (seq_start, "seq_start"), (seq_pos0, "seq_pos0"), (slots, "slots")):
         _need(t, nm, torch.int32, 1)
+    if tile_row0 is not None:
+        _need(tile_row0, "tile_row0", torch.int32, 1)
+    elif splits <= 1:
+        raise KernelError("sigmoid_attention_prefill: only a step whose pages are dealt out may leave tile_row0 out")
     _need(page_table, "page_table", torch.int32, 2)
     _need(k_cache, "k_cache", q.dtype, 4)
     _need(v_cache, "v_cache", q.dtype, 4)
@@ -1472,12 +1480,17 @@ def sigmoid_attention_prefill(q: torch.Tensor, q_stride: int, out: torch.Tensor,
         need = n_heads if gate_per_head else n_heads * v_dim
         if not gate.is_cuda or gate.dtype != q.dtype or gate.stride(-1) != 1 or gate.shape[-1] < need or gate_stride <= 0:
             raise KernelError("sigmoid_attention_prefill: gate must be a CUDA view of q's type with unit inner stride that holds the gates")
+    part = None
+    if splits > 1:
+        part = torch.empty(out.shape[0] * splits * n_heads * v_dim, dtype=torch.float32, device=q.device)
+        global LAUNCHES
+        LAUNCHES += 1  # the kernel that adds the splits up
     _check(_fn("sigmoid_attention_prefill", "bn_sigmoid_attention_prefill")(
         _ptr(q), int(q_stride), _ptr(out), int(out.shape[1]), int(tile_seq.shape[0]), int(n_heads), int(n_kv_heads), int(head_dim),
         int(v_dim), c_float(scale), int(window), _ptr(rel), int(n_rel), _ptr(mix),
         c_void_p(gate.data_ptr()) if gate is not None else _NULL, int(gate_stride), int(gate_mode), _ptr(tile_seq), _ptr(tile_row0),
         _ptr(seq_start), _ptr(seq_pos0), _ptr(slots), _ptr(page_table), int(page_table.shape[1]), _ptr(k_cache), _ptr(v_cache),
-        _stream()), "sigmoid_attention_prefill")
+        _ptr(part), int(max(1, splits)), int(out.shape[0]), _stream()), "sigmoid_attention_prefill")
     return out
 
 

@@ -38,7 +38,8 @@ __device__ __forceinline__ unsigned sp_map(unsigned local_addr, unsigned rank) {
 }
 __device__ __forceinline__ float2 sp_ld2(unsigned cluster_addr) {
   float2 v;
-  asm volatile("ld.shared::cluster.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(cluster_addr) : "memory");
+  // volatile keeps it between the cluster barriers (which clobber memory); without a clobber of its own several may be in flight
+  asm volatile("ld.shared::cluster.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(cluster_addr));
   return v;
 }
 __device__ __forceinline__ float sp_rest(float p) { return p - __bfloat162float(__float2bfloat16_rn(p)); }
@@ -58,6 +59,8 @@ struct SpArgs {
   const int *tile_seq, *tile_row0, *seq_start, *seq_pos0, *slots, *page_table;
   int pt_stride;
   const __nv_bfloat16 *k_cache, *v_cache;
+  float* part;   // not null: the pages of a block of rows are dealt out over n_splits clusters (blockIdx.z), which
+  int n_splits;  // leave their sums here, float32 [tokens][n_splits][n_heads * v_dim], for the kernel that adds them up
 };
 
 template <int HD, int VD, int WPH>
@@ -85,7 +88,8 @@ sigmoid_attention_prefill_kernel(const SpArgs a) {
   const unsigned s_a_addr = (unsigned)__cvta_generic_to_shared(s_a);
 
   const int blk = gridDim.y - 1 - blockIdx.y;
-  const int seq = a.tile_seq[blk], row0 = a.tile_row0[blk] + blockIdx.z * SP_M;
+  const int seq = a.tile_seq[blk], row0 = (a.tile_row0 ? a.tile_row0[blk] : 0) + (a.part ? 0 : blockIdx.z * SP_M);
+  const int split = a.part ? blockIdx.z : 0, stride = a.part ? a.n_splits : 1;
   const int start = a.seq_start[seq], n_new = a.seq_start[seq + 1] - start, pos0 = a.seq_pos0[seq];
   if (row0 >= n_new) return;  // the whole cluster alike
   const int* pt = a.page_table + (size_t)a.slots[seq] * a.pt_stride;
@@ -93,7 +97,8 @@ sigmoid_attention_prefill_kernel(const SpArgs a) {
   const int seq_last = pos0 + n_new - 1;
   const int q_first = pos0 + row0, q_last = q_first + rows_here - 1;
   const int lo_first = a.window > 0 ? max(0, q_first - a.window + 1) : 0;
-  const int tile_lo = lo_first / SP_N, n_walk = q_last / SP_N - tile_lo + 1;
+  const int tile_lo = lo_first / SP_N + split;
+  const int n_walk = max(0, (q_last / SP_N - tile_lo + stride) / stride);  // pages tile_lo, tile_lo + stride, ...
   const int real_chunks = a.head_dim / 8, real_vchunks = a.v_dim / 8;
 
   // ---- queries: through shared memory (the mixed weights' place) into A fragments
@@ -138,7 +143,7 @@ sigmoid_attention_prefill_kernel(const SpArgs a) {
       cp_async16(s_v + stage * VTILE + sp_off<VD>(r, ch), ok ? vb + (size_t)r * a.v_dim + ch * 8 : vb, ok);
     }
   };
-  load_kv(tile_lo, 0);
+  if (n_walk > 0) load_kv(tile_lo, 0);
   cp_async_commit();
 
   float o[NO][4];
@@ -156,11 +161,11 @@ sigmoid_attention_prefill_kernel(const SpArgs a) {
   float* my_bias = s_bias + warp * SP_BIAS;
 
   for (int u = 0; u < n_walk; ++u) {
-    const int tile = tile_lo + u, stage = u & 1;
+    const int tile = tile_lo + u * stride, stage = u & 1;
     cp_async_wait<0>();
     __syncthreads();  // this page is here; everybody is done with the other stage and with the mixed weights
     if (u + 1 < n_walk) {
-      load_kv(tile + 1, stage ^ 1);
+      load_kv(tile + stride, stage ^ 1);
       cp_async_commit();
     }
     const int dist0 = q_first - (tile * SP_N + SP_N - 1);
@@ -197,7 +202,7 @@ sigmoid_attention_prefill_kernel(const SpArgs a) {
           const bool ok = kpos <= qpos[e] && kpos >= qlo[e];
           float z = s[j][2 * e + x] * a.scale;
           if (a.rel && ok) z += my_bias[qpos[e] - kpos - dist0];
-          w2[x] = ok ? 1.0f / (1.0f + expf(-z)) : 0.f;
+          w2[x] = ok ? __fdividef(1.0f, 1.0f + __expf(-z)) : 0.f;
         }
         *reinterpret_cast<float2*>(my_a + (g4 + e * 8) * SP_LD + (wq * NJ + j) * 8 + 2 * t4) = make_float2(w2[0], w2[1]);
       }
@@ -210,21 +215,33 @@ sigmoid_attention_prefill_kernel(const SpArgs a) {
 #pragma unroll
       for (int r = 0; r < SP_MAX_R; ++r) acc[r][0] = acc[r][1] = acc[r][2] = acc[r][3] = 0.f;
       const unsigned at = (unsigned)((g4 * SP_LD + j * 8 + 2 * t4) * 4);
+      // up to four heads' weights of a block are asked for at a time (eight loads in flight), then mixed in
       for (int cg = 0; cg < a.n_kv_heads; ++cg) {
         const unsigned base = sp_map(s_a_addr, (unsigned)cg) + at;
-        for (int rg = 0; rg < R; ++rg) {
-          const float2 lo = sp_ld2(base + (unsigned)(rg * SP_M * SP_LD * 4));
-          const float2 hi = sp_ld2(base + (unsigned)((rg * SP_M + 8) * SP_LD * 4));
-          const float4 m0 = *reinterpret_cast<const float4*>(s_mix + (cg * R + rg) * SP_MAX_R);
-          const float4 m1 = *reinterpret_cast<const float4*>(s_mix + (cg * R + rg) * SP_MAX_R + 4);
-          const float m[SP_MAX_R] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
+        for (int rg0 = 0; rg0 < R; rg0 += 4) {
+          float2 lo[4], hi[4];
 #pragma unroll
-          for (int r = 0; r < SP_MAX_R; ++r) {
-            if (r < R) {
-              acc[r][0] = fmaf(m[r], lo.x, acc[r][0]);
-              acc[r][1] = fmaf(m[r], lo.y, acc[r][1]);
-              acc[r][2] = fmaf(m[r], hi.x, acc[r][2]);
-              acc[r][3] = fmaf(m[r], hi.y, acc[r][3]);
+          for (int x = 0; x < 4; ++x) {
+            const unsigned addr = base + (unsigned)(min(rg0 + x, R - 1) * SP_M * SP_LD * 4);
+            lo[x] = sp_ld2(addr);
+            hi[x] = sp_ld2(addr + (unsigned)(8 * SP_LD * 4));
+          }
+#pragma unroll
+          for (int x = 0; x < 4; ++x) {
+            if (rg0 + x < R) {
+              const float* mrow = s_mix + (cg * R + rg0 + x) * SP_MAX_R;
+              const float4 m0 = *reinterpret_cast<const float4*>(mrow);
+              const float4 m1 = *reinterpret_cast<const float4*>(mrow + 4);
+              const float m[SP_MAX_R] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
+#pragma unroll
+              for (int r = 0; r < SP_MAX_R; ++r) {
+                if (r < R) {
+                  acc[r][0] = fmaf(m[r], lo[x].x, acc[r][0]);
+                  acc[r][1] = fmaf(m[r], lo[x].y, acc[r][1]);
+                  acc[r][2] = fmaf(m[r], hi[x].x, acc[r][2]);
+                  acc[r][3] = fmaf(m[r], hi[x].y, acc[r][3]);
+                }
+              }
             }
           }
         }
@@ -262,7 +279,21 @@ sigmoid_attention_prefill_kernel(const SpArgs a) {
       }
     }
   }
-  sp_cluster_wait();  // no block leaves while another still reads its weights
+  if (n_walk > 0) sp_cluster_wait();  // no block leaves while another still reads its weights
+  if (a.part) {
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int r = g4 + e * 8;
+      if (r >= rows_here) continue;
+      float* prow = a.part + ((size_t)(start + row0 + r) * a.n_splits + split) * H * a.v_dim + (size_t)h * a.v_dim;
+#pragma unroll
+      for (int j = 0; j < NO; ++j) {
+        const int d = (wq * NO + j) * 8 + 2 * t4;
+        if (d < a.v_dim) *reinterpret_cast<float2*>(prow + d) = make_float2(o[j][2 * e], o[j][2 * e + 1]);
+      }
+    }
+    return;
+  }
 
   // ---- gate and store
 #pragma unroll
@@ -290,6 +321,21 @@ sigmoid_attention_prefill_kernel(const SpArgs a) {
   }
 }
 
+// out[t][i] = gate * sum_z part[t][z][i]
+__global__ void sigmoid_attention_sum_kernel(const float* __restrict__ part, int n_splits, int row, int v_dim,
+                                             const __nv_bfloat16* __restrict__ gate, int gate_stride, int gate_mode,
+                                             __nv_bfloat16* __restrict__ out, int out_stride) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  for (int i = threadIdx.x; i < row; i += blockDim.x) {
+    float s = 0.f;
+    for (int z = 0; z < n_splits; ++z) s += part[((size_t)t * n_splits + z) * row + i];
+    if (gate_mode) s *= 1.0f / (1.0f + expf(-__bfloat162float(gate[(size_t)t * gate_stride + (gate_mode == 1 ? i / v_dim : i)])));
+    out[(size_t)t * out_stride + i] = __float2bfloat16_rn(s);
+  }
+}
+
 // Warps per query head: so that a block has about eight warps.
 static int sp_wph(int R) { return R <= 2 ? 4 : (R <= 4 ? 2 : 1); }
 
@@ -308,8 +354,9 @@ static int sp_launch_w(const SpArgs& a, int n_tiles, cudaStream_t stream) {
     if (e != cudaSuccess) return BN_ERR_LAUNCH + (int)e;
     granted = smem;
   }
-  // one cluster per 16 rows: the blocks of 64 rows of the step's list, four deep
-  dim3 grid(a.n_kv_heads, n_tiles, 64 / SP_M);
+  // one cluster per 16 rows: the blocks of 64 rows of the step's list, four deep; or, with the pages dealt out,
+  // one cluster per block of (at most 16) rows and share of the pages
+  dim3 grid(a.n_kv_heads, n_tiles, a.part ? a.n_splits : 64 / SP_M);
   cudaError_t e = bn_launch_cluster(sigmoid_attention_prefill_kernel<HD, VD, WPH>, grid, dim3(32 * R * WPH), smem, stream,
                                     dim3(a.n_kv_heads, 1, 1), a);
   if (e != cudaSuccess) return BN_ERR_LAUNCH + (int)e;
@@ -339,13 +386,18 @@ extern "C" int bn_sigmoid_attention_prefill_fits(int n_heads, int n_kv_heads, in
 // [n_seqs + 1]: first packed row of each sequence; seq_pos0: its length before the step.  rel [n_rel, n_heads]
 // float32 by distance (the last row for every longer one) or null; mix [n_heads, n_heads] float32 or null;
 // gate_mode 0 none, 1 one number per head, 2 one per output number (logistic function applied here).
+// n_splits > 1 (every listed block of rows then holds at most 16 rows, tile_row0 may be null for rows from 0 on):
+// the pages a block of rows sees are dealt out over so many clusters, whose float32 sums in part
+// [n_tokens, n_splits, n_heads * v_dim] a second kernel adds up: for steps of few tokens behind long contexts.
 extern "C" int bn_sigmoid_attention_prefill(const void* q, int q_stride, void* out, int out_stride, int n_tiles, int n_heads,
                                             int n_kv_heads, int head_dim, int v_dim, float scale, int window, const float* rel,
                                             int n_rel, const float* mix, const void* gate, int gate_stride, int gate_mode,
                                             const int* tile_seq, const int* tile_row0, const int* seq_start, const int* seq_pos0,
                                             const int* slots, const int* page_table, int pt_stride, const void* k_cache,
-                                            const void* v_cache, cudaStream_t stream) {
+                                            const void* v_cache, float* part, int n_splits, int n_tokens, cudaStream_t stream) {
   if (n_tiles <= 0) return BN_OK;
+  if (n_splits < 1 || n_splits > 65535 || (n_splits > 1 && (!part || n_tokens <= 0))) return BN_ERR_BAD_ARG;
+  if (n_splits == 1) part = nullptr;
   if (!bn_sigmoid_attention_prefill_fits(n_heads, n_kv_heads, head_dim, v_dim) || n_tiles > 65535 || !q || !out || !k_cache || !v_cache ||
       window < 0 || (q_stride % 8) || (out_stride % 2) || (((uintptr_t)q) & 15) || (rel && n_rel <= 0) || gate_mode < 0 || gate_mode > 2 ||
       (gate_mode && (!gate || (gate_stride % 2) || (((uintptr_t)gate) & 3))))
@@ -357,9 +409,16 @@ extern "C" int bn_sigmoid_attention_prefill(const void* q, int q_stride, void* o
   a.gate_mode = gate_mode; a.tile_seq = tile_seq; a.tile_row0 = tile_row0; a.seq_start = seq_start; a.seq_pos0 = seq_pos0;
   a.slots = slots; a.page_table = page_table; a.pt_stride = pt_stride;
   a.k_cache = (const __nv_bfloat16*)k_cache; a.v_cache = (const __nv_bfloat16*)v_cache;
+  a.part = part; a.n_splits = n_splits;
   const bool k64 = head_dim <= 64, v64 = v_dim <= 64;
-  if (k64 && v64) return sp_launch<64, 64>(a, n_tiles, stream);
-  if (k64) return sp_launch<64, 128>(a, n_tiles, stream);
-  if (v64) return sp_launch<128, 64>(a, n_tiles, stream);
-  return sp_launch<128, 128>(a, n_tiles, stream);
+  int rc;
+  if (k64 && v64) rc = sp_launch<64, 64>(a, n_tiles, stream);
+  else if (k64) rc = sp_launch<64, 128>(a, n_tiles, stream);
+  else if (v64) rc = sp_launch<128, 64>(a, n_tiles, stream);
+  else rc = sp_launch<128, 128>(a, n_tiles, stream);
+  if (rc != BN_OK || !part) return rc;
+  BN_LAUNCH(sigmoid_attention_sum_kernel, n_tokens, 256, 0, stream, (const float*)part, n_splits, n_heads * v_dim, v_dim, a.gate, gate_stride,
+            gate_mode, a.out, out_stride);
+  BN_CHECK_LAUNCH();
+  return BN_OK;
 }

@@ -7,6 +7,7 @@ from typing import Dict, Optional
 import torch
 
 from ..csrc import ops
+from ..csrc.ops import PAGE
 from .base import KvRequest, Mixer, ParamSpec
 from .registry import register_mixer
 
@@ -26,6 +27,7 @@ class SigmoidAttention(Mixer):
     kernels = ("linear", "linear_mma", "linear_tc", "gemm_tc", "unit_norm", "sigmoid_attention", "sigmoid_attention_prefill")
     graph_safe = True
     TILED_MIN_TOKENS = 16  # a sequence brings at least so many new tokens: the tensor-core kernel runs
+    TILED_DECODE = True    # steps of one token per sequence take it too (where its sizes fit), pages dealt out over clusters
 
     def __init__(self, spec, build):
         super().__init__(spec, build)
@@ -133,8 +135,18 @@ class SigmoidAttention(Mixer):
             ctx.tap("attn_q", lambda: proj[:, : self.q_dim])
         out = torch.empty((n, self.o_dim), dtype=self.build.dtype, device=h.device)
         gate = proj[:, self.g_off:] if s.output_gate else None
-        if (self.build.dtype == torch.bfloat16 and not ctx.decode and ctx.tile_seq is not None and ctx.max_new >= self.TILED_MIN_TOKENS
-                and self.tiled_fits):
+        if self.tiled_fits and ctx.decode and self.TILED_DECODE:
+            # one token per sequence: a cluster per sequence and share of its pages; a block of rows is one row
+            visible = min(ctx.max_len, s.window) if s.window > 0 else ctx.max_len
+            pages = -(-visible // PAGE) + 1  # a window may begin and end inside a page
+            splits = max(1, min(pages, 2 * ops.n_sms(h.device) // (n * s.n_kv_heads)))
+            ops.sigmoid_attention_prefill(proj, self.row, out, s.n_heads, s.n_kv_heads, s.head_dim, s.scale, s.window, ctx.tok_seq,
+                                          None if splits > 1 else torch.zeros_like(ctx.tok_seq), ctx.seq_start, ctx.seq_pos0, ctx.slots,
+                                          kv.page_table, kv.k, kv.v, rel=self.rel, mix=self.mix, gate=gate, gate_stride=self.row,
+                                          splits=splits)
+            ctx.tap("attn_out", out)
+            return ops.linear(out, self.w_o, out_dtype=torch.float32)
+        if (self.tiled_fits and not ctx.decode and ctx.tile_seq is not None and ctx.max_new >= self.TILED_MIN_TOKENS):
             ops.sigmoid_attention_prefill(proj, self.row, out, s.n_heads, s.n_kv_heads, s.head_dim, s.scale, s.window, ctx.tile_seq,
                                           ctx.tile_row0, ctx.seq_start, ctx.seq_pos0, ctx.slots, kv.page_table, kv.k, kv.v,
                                           rel=self.rel, mix=self.mix, gate=gate, gate_stride=self.row)

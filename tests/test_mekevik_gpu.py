@@ -122,13 +122,16 @@ def test_attention_without_a_softmax_over_the_pages(cuda_device, dtype, shape):
             assert dtype != "bfloat16" or d % 16 or dv % 16, "these sizes should fit the kernel for runs of tokens"
             continue
         tiles = [(s_, r) for s_, c_ in enumerate(new) for r in range(0, c_, 64)]
-        out = torch.full((len(rows), H * dv), float("nan"), dtype=t, device="cuda")
-        ops.sigmoid_attention_prefill(qd, qd.shape[1], out, H, G, d, m["scale"], window, ints(s_ for s_, _ in tiles), ints(r for _, r in tiles),
-                                      ints(np.concatenate([[0], np.cumsum(new)])), ints(l - c_ for l, c_ in zip(lens, new)), ints([1, 2, 3]),
-                                      table, kc, vc, rel=rel, mix=talk, gate=gd, gate_stride=gd.shape[1])
-        got = out.float().cpu().numpy()
-        err = np.abs(got - want[rows]).max(axis=1) / np.maximum(1.0, np.abs(want[rows]).max(axis=1))
-        assert np.isfinite(got).all() and err.max() < tol, f"{what}, runs of tokens: row {int(np.argmax(err))} (position {pos[int(np.argmax(err))]}) off by {err.max():.3e}"
+        for splits in ((1, 2, 5) if what == "single" else (1,)):  # single tokens also with their pages dealt out over clusters
+            out = torch.full((len(rows), H * dv), float("nan"), dtype=t, device="cuda")
+            ops.sigmoid_attention_prefill(qd, qd.shape[1], out, H, G, d, m["scale"], window, ints(s_ for s_, _ in tiles),
+                                          None if splits > 1 else ints(r for _, r in tiles), ints(np.concatenate([[0], np.cumsum(new)])),
+                                          ints(l - c_ for l, c_ in zip(lens, new)), ints([1, 2, 3]), table, kc, vc, rel=rel, mix=talk, gate=gd,
+                                          gate_stride=gd.shape[1], splits=splits)
+            got = out.float().cpu().numpy()
+            err = np.abs(got - want[rows]).max(axis=1) / np.maximum(1.0, np.abs(want[rows]).max(axis=1))
+            assert np.isfinite(got).all() and err.max() < tol, \
+                f"{what}, runs of tokens, {splits} splits: row {int(np.argmax(err))} (position {pos[int(np.argmax(err))]}) off by {err.max():.3e}"
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
