@@ -63,9 +63,12 @@ struct SpArgs {
   int n_splits;  // leave their sums here, float32 [tokens][n_splits][n_heads * v_dim], for the kernel that adds them up
 };
 
-template <int HD, int VD, int WPH>
-__global__ void __launch_bounds__(32 * SP_MAX_R, WPH > 1 ? 2 : 1)
+// RP: the query heads per key/value head, rounded up to a power of two (the mixing keeps so many accumulators
+// per column); the warps per query head follow from it, so that a block has about eight warps.
+template <int HD, int VD, int RP>
+__global__ void __launch_bounds__(32 * SP_MAX_R, RP <= 4 ? 2 : 1)
 sigmoid_attention_prefill_kernel(const SpArgs a) {
+  constexpr int WPH = RP <= 2 ? 4 : (RP <= 4 ? 2 : 1);
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ __align__(128) unsigned char smem[];
@@ -211,9 +214,9 @@ sigmoid_attention_prefill_kernel(const SpArgs a) {
     sp_cluster_wait();  // all heads' weights of this page are written
     // ---- mixing: this warp's column groups, all heads in, this block's heads out
     for (int j = warp; j < SP_N / 8; j += n_warps) {
-      float acc[SP_MAX_R][4];
+      float acc[RP][4];
 #pragma unroll
-      for (int r = 0; r < SP_MAX_R; ++r) acc[r][0] = acc[r][1] = acc[r][2] = acc[r][3] = 0.f;
+      for (int r = 0; r < RP; ++r) acc[r][0] = acc[r][1] = acc[r][2] = acc[r][3] = 0.f;
       const unsigned at = (unsigned)((g4 * SP_LD + j * 8 + 2 * t4) * 4);
       // up to four heads' weights of a block are asked for at a time (eight loads in flight), then mixed in
       for (int cg = 0; cg < a.n_kv_heads; ++cg) {
@@ -229,25 +232,24 @@ sigmoid_attention_prefill_kernel(const SpArgs a) {
 #pragma unroll
           for (int x = 0; x < 4; ++x) {
             if (rg0 + x < R) {
+              // the factors of heads beyond R are zeros
               const float* mrow = s_mix + (cg * R + rg0 + x) * SP_MAX_R;
-              const float4 m0 = *reinterpret_cast<const float4*>(mrow);
-              const float4 m1 = *reinterpret_cast<const float4*>(mrow + 4);
-              const float m[SP_MAX_R] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
+              float m[SP_MAX_R];
+              *reinterpret_cast<float4*>(m) = *reinterpret_cast<const float4*>(mrow);
+              if (RP > 4) *reinterpret_cast<float4*>(m + 4) = *reinterpret_cast<const float4*>(mrow + 4);
 #pragma unroll
-              for (int r = 0; r < SP_MAX_R; ++r) {
-                if (r < R) {
-                  acc[r][0] = fmaf(m[r], lo[x].x, acc[r][0]);
-                  acc[r][1] = fmaf(m[r], lo[x].y, acc[r][1]);
-                  acc[r][2] = fmaf(m[r], hi[x].x, acc[r][2]);
-                  acc[r][3] = fmaf(m[r], hi[x].y, acc[r][3]);
-                }
+              for (int r = 0; r < RP; ++r) {
+                acc[r][0] = fmaf(m[r], lo[x].x, acc[r][0]);
+                acc[r][1] = fmaf(m[r], lo[x].y, acc[r][1]);
+                acc[r][2] = fmaf(m[r], hi[x].x, acc[r][2]);
+                acc[r][3] = fmaf(m[r], hi[x].y, acc[r][3]);
               }
             }
           }
         }
       }
 #pragma unroll
-      for (int r = 0; r < SP_MAX_R; ++r) {
+      for (int r = 0; r < RP; ++r) {
         if (r < R) {
           float* wr = s_w + r * SP_M * SP_LD + j * 8 + 2 * t4;
           *reinterpret_cast<float2*>(wr + g4 * SP_LD) = make_float2(acc[r][0], acc[r][1]);
@@ -336,7 +338,7 @@ __global__ void sigmoid_attention_sum_kernel(const float* __restrict__ part, int
   }
 }
 
-// Warps per query head: so that a block has about eight warps.
+// Warps per query head: so that a block has about eight warps (the kernel's WPH).
 static int sp_wph(int R) { return R <= 2 ? 4 : (R <= 4 ? 2 : 1); }
 
 static size_t sp_smem_bytes(int hd, int vd, int n_heads, int R) {
@@ -344,20 +346,21 @@ static size_t sp_smem_bytes(int hd, int vd, int n_heads, int R) {
          ((size_t)2 * R * SP_M * SP_LD + (size_t)n_heads * SP_MAX_R + (size_t)R * sp_wph(R) * SP_BIAS) * sizeof(float);
 }
 
-template <int HD, int VD, int WPH>
+template <int HD, int VD, int RP>
 static int sp_launch_w(const SpArgs& a, int n_tiles, cudaStream_t stream) {
+  const int WPH = sp_wph(RP);
   const int R = a.n_heads / a.n_kv_heads;
   const size_t smem = sp_smem_bytes(HD, VD, a.n_heads, R);
   static size_t granted = 0;
   if (smem > granted) {
-    cudaError_t e = cudaFuncSetAttribute(sigmoid_attention_prefill_kernel<HD, VD, WPH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(sigmoid_attention_prefill_kernel<HD, VD, RP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return BN_ERR_LAUNCH + (int)e;
     granted = smem;
   }
   // one cluster per 16 rows: the blocks of 64 rows of the step's list, four deep; or, with the pages dealt out,
   // one cluster per block of (at most 16) rows and share of the pages
   dim3 grid(a.n_kv_heads, n_tiles, a.part ? a.n_splits : 64 / SP_M);
-  cudaError_t e = bn_launch_cluster(sigmoid_attention_prefill_kernel<HD, VD, WPH>, grid, dim3(32 * R * WPH), smem, stream,
+  cudaError_t e = bn_launch_cluster(sigmoid_attention_prefill_kernel<HD, VD, RP>, grid, dim3(32 * R * WPH), smem, stream,
                                     dim3(a.n_kv_heads, 1, 1), a);
   if (e != cudaSuccess) return BN_ERR_LAUNCH + (int)e;
   BN_CHECK_LAUNCH();
@@ -366,10 +369,11 @@ static int sp_launch_w(const SpArgs& a, int n_tiles, cudaStream_t stream) {
 
 template <int HD, int VD>
 static int sp_launch(const SpArgs& a, int n_tiles, cudaStream_t stream) {
-  const int wph = sp_wph(a.n_heads / a.n_kv_heads);
-  if (wph == 4) return sp_launch_w<HD, VD, 4>(a, n_tiles, stream);
-  if (wph == 2) return sp_launch_w<HD, VD, 2>(a, n_tiles, stream);
-  return sp_launch_w<HD, VD, 1>(a, n_tiles, stream);
+  const int R = a.n_heads / a.n_kv_heads;
+  if (R == 1) return sp_launch_w<HD, VD, 1>(a, n_tiles, stream);
+  if (R == 2) return sp_launch_w<HD, VD, 2>(a, n_tiles, stream);
+  if (R <= 4) return sp_launch_w<HD, VD, 4>(a, n_tiles, stream);
+  return sp_launch_w<HD, VD, 8>(a, n_tiles, stream);
 }
 
 // Whether the sizes fit this kernel (1) or want the general one (0): bfloat16 rows in whole 16-element steps up
