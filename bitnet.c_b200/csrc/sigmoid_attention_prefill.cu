@@ -36,10 +36,10 @@ __device__ __forceinline__ unsigned sp_map(unsigned local_addr, unsigned rank) {
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
   return remote;
 }
-__device__ __forceinline__ float2 sp_ld2(unsigned cluster_addr) {
-  float2 v;
-  // volatile keeps it between the cluster barriers (which clobber memory); without a clobber of its own several may be in flight
-  asm volatile("ld.shared::cluster.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(cluster_addr));
+// volatile keeps it between the cluster barriers (which clobber memory); without a clobber of its own several may be in flight
+__device__ __forceinline__ float4 sp_ld4(unsigned cluster_addr) {
+  float4 v;
+  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(cluster_addr));
   return v;
 }
 __device__ __forceinline__ float sp_rest(float p) { return p - __bfloat162float(__float2bfloat16_rn(p)); }
@@ -130,8 +130,9 @@ sigmoid_attention_prefill_kernel(const SpArgs a) {
   }
   __syncthreads();  // the mixed weights' place is free again
 
-  auto load_kv = [&](int tile, int stage) {
-    const int page = pt[tile];
+  // the page's number is asked for one page ahead of its rows, the bias of a page's distances one page ahead of
+  // its scores: no warp waits for either
+  auto load_kv = [&](int tile, int page, int stage) {
     const __nv_bfloat16* kb = a.k_cache + ((size_t)page * a.n_kv_heads + c) * BN_PAGE * a.head_dim;
     const __nv_bfloat16* vb = a.v_cache + ((size_t)page * a.n_kv_heads + c) * BN_PAGE * a.v_dim;
     for (int p = tid; p < SP_N * CHUNKS; p += n_threads) {
@@ -146,8 +147,18 @@ sigmoid_attention_prefill_kernel(const SpArgs a) {
       cp_async16(s_v + stage * VTILE + sp_off<VD>(r, ch), ok ? vb + (size_t)r * a.v_dim + ch * 8 : vb, ok);
     }
   };
-  if (n_walk > 0) load_kv(tile_lo, 0);
+  if (n_walk > 0) load_kv(tile_lo, pt[tile_lo], 0);
   cp_async_commit();
+  int page_next = n_walk > 1 ? pt[tile_lo + stride] : 0;
+  auto bias_of = [&](int tile, int x) {  // of distance (q_first - the tile's last key) + lane + 32 x, for this warp's head
+    const int dist = q_first - (tile * SP_N + SP_N - 1) + lane + 32 * x;
+    return a.rel[(size_t)min(max(dist, 0), a.n_rel - 1) * H + h];
+  };
+  float bias_next[3] = {0.f, 0.f, 0.f};
+  if (a.rel && n_walk > 0) {
+#pragma unroll
+    for (int x = 0; x < 3; ++x) bias_next[x] = bias_of(tile_lo, x);
+  }
 
   float o[NO][4];
 #pragma unroll
@@ -168,13 +179,20 @@ sigmoid_attention_prefill_kernel(const SpArgs a) {
     cp_async_wait<0>();
     __syncthreads();  // this page is here; everybody is done with the other stage and with the mixed weights
     if (u + 1 < n_walk) {
-      load_kv(tile + stride, stage ^ 1);
+      load_kv(tile + stride, page_next, stage ^ 1);
       cp_async_commit();
+      if (u + 2 < n_walk) page_next = pt[tile + 2 * stride];
     }
     const int dist0 = q_first - (tile * SP_N + SP_N - 1);
     if (a.rel) {
-      for (int i = lane; i < SP_BIAS; i += 32) my_bias[i] = a.rel[(size_t)min(max(dist0 + i, 0), a.n_rel - 1) * H + h];
+#pragma unroll
+      for (int x = 0; x < 3; ++x)
+        if (lane + 32 * x < SP_BIAS) my_bias[lane + 32 * x] = bias_next[x];
       __syncwarp();
+      if (u + 1 < n_walk) {
+#pragma unroll
+        for (int x = 0; x < 3; ++x) bias_next[x] = bias_of(tile + stride, x);
+      }
     }
     // ---- scores of this warp's head and keys
     float s[NJ][4];
@@ -213,22 +231,20 @@ sigmoid_attention_prefill_kernel(const SpArgs a) {
     sp_cluster_arrive();
     sp_cluster_wait();  // all heads' weights of this page are written
     // ---- mixing: this warp's column groups, all heads in, this block's heads out
+    // a lane takes four neighbouring keys of one row: a 16 x 8 group of a head is one 16-byte read per lane
     for (int j = warp; j < SP_N / 8; j += n_warps) {
       float acc[RP][4];
 #pragma unroll
       for (int r = 0; r < RP; ++r) acc[r][0] = acc[r][1] = acc[r][2] = acc[r][3] = 0.f;
-      const unsigned at = (unsigned)((g4 * SP_LD + j * 8 + 2 * t4) * 4);
-      // up to four heads' weights of a block are asked for at a time (eight loads in flight), then mixed in
+      const int at_f = (lane >> 1) * SP_LD + j * 8 + (lane & 1) * 4;
+      const unsigned at = (unsigned)(at_f * 4);
+      // up to four heads' weights of a block are asked for at a time, then mixed in
       for (int cg = 0; cg < a.n_kv_heads; ++cg) {
         const unsigned base = sp_map(s_a_addr, (unsigned)cg) + at;
         for (int rg0 = 0; rg0 < R; rg0 += 4) {
-          float2 lo[4], hi[4];
+          float4 v[4];
 #pragma unroll
-          for (int x = 0; x < 4; ++x) {
-            const unsigned addr = base + (unsigned)(min(rg0 + x, R - 1) * SP_M * SP_LD * 4);
-            lo[x] = sp_ld2(addr);
-            hi[x] = sp_ld2(addr + (unsigned)(8 * SP_LD * 4));
-          }
+          for (int x = 0; x < 4; ++x) v[x] = sp_ld4(base + (unsigned)(min(rg0 + x, R - 1) * SP_M * SP_LD * 4));
 #pragma unroll
           for (int x = 0; x < 4; ++x) {
             if (rg0 + x < R) {
@@ -239,23 +255,18 @@ sigmoid_attention_prefill_kernel(const SpArgs a) {
               if (RP > 4) *reinterpret_cast<float4*>(m + 4) = *reinterpret_cast<const float4*>(mrow + 4);
 #pragma unroll
               for (int r = 0; r < RP; ++r) {
-                acc[r][0] = fmaf(m[r], lo[x].x, acc[r][0]);
-                acc[r][1] = fmaf(m[r], lo[x].y, acc[r][1]);
-                acc[r][2] = fmaf(m[r], hi[x].x, acc[r][2]);
-                acc[r][3] = fmaf(m[r], hi[x].y, acc[r][3]);
+                acc[r][0] = fmaf(m[r], v[x].x, acc[r][0]);
+                acc[r][1] = fmaf(m[r], v[x].y, acc[r][1]);
+                acc[r][2] = fmaf(m[r], v[x].z, acc[r][2]);
+                acc[r][3] = fmaf(m[r], v[x].w, acc[r][3]);
               }
             }
           }
         }
       }
 #pragma unroll
-      for (int r = 0; r < RP; ++r) {
-        if (r < R) {
-          float* wr = s_w + r * SP_M * SP_LD + j * 8 + 2 * t4;
-          *reinterpret_cast<float2*>(wr + g4 * SP_LD) = make_float2(acc[r][0], acc[r][1]);
-          *reinterpret_cast<float2*>(wr + (g4 + 8) * SP_LD) = make_float2(acc[r][2], acc[r][3]);
-        }
-      }
+      for (int r = 0; r < RP; ++r)
+        if (r < R) *reinterpret_cast<float4*>(s_w + r * SP_M * SP_LD + at_f) = make_float4(acc[r][0], acc[r][1], acc[r][2], acc[r][3]);
     }
     sp_cluster_arrive();  // this block reads no other's weights of this page any more
     __syncthreads();      // the mixed weights of all column groups are written
