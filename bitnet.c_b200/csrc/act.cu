@@ -162,6 +162,29 @@ __global__ void glu_halves_kernel(const T* __restrict__ h, T* __restrict__ out, 
   out[idx] = from_f32<T>(glu_activation(to_f32<T>(h[t * 2 * inter + j]), act) * to_f32<T>(h[t * 2 * inter + inter + j]));
 }
 
+// inter a multiple of 8, both buffers 16-byte aligned: a thread takes 8 gate and 8 up values in 16-byte pieces
+__global__ void glu_halves_bf16x8_kernel(const __nv_bfloat16* __restrict__ h, __nv_bfloat16* __restrict__ out, int inter,
+                                         size_t total8, int act) {
+  pdl_launch_dependents();
+  pdl_wait();
+  size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total8) return;
+  const int per_row = inter / 8;
+  size_t t = idx / per_row;
+  size_t j = (idx - t * per_row) * 8;
+  uint4 gr = *reinterpret_cast<const uint4*>(h + t * 2 * inter + j), ur = *reinterpret_cast<const uint4*>(h + t * 2 * inter + inter + j);
+  const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&gr);
+  const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&ur);
+  uint4 res;
+  __nv_bfloat162* r2 = reinterpret_cast<__nv_bfloat162*>(&res);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 g = __bfloat1622float2(g2[i]), u = __bfloat1622float2(u2[i]);
+    r2[i] = __floats2bfloat162_rn(glu_activation(g.x, act) * u.x, glu_activation(g.y, act) * u.y);
+  }
+  *reinterpret_cast<uint4*>(out + t * inter + j) = res;
+}
+
 extern "C" int bn_glu_halves(const void* h, void* out, int dtype, int n_rows, int inter, int act, cudaStream_t stream) {
   if (n_rows <= 0) return BN_OK;
   if (inter <= 0 || !h || !out || (act != BN_ACT_SILU && act != BN_ACT_GELU_TANH)) return BN_ERR_BAD_ARG;
@@ -169,6 +192,9 @@ extern "C" int bn_glu_halves(const void* h, void* out, int dtype, int n_rows, in
   unsigned blocks = (unsigned)((total + 255) / 256);
   if (dtype == BN_F32)
     BN_LAUNCH(glu_halves_kernel<float>, blocks, 256, 0, stream, (const float*)h, (float*)out, inter, total, act);
+  else if (dtype == BN_BF16 && inter % 8 == 0 && ((((uintptr_t)h) | ((uintptr_t)out)) & 15) == 0)
+    BN_LAUNCH(glu_halves_bf16x8_kernel, (unsigned)((total / 8 + 255) / 256), 256, 0, stream, (const __nv_bfloat16*)h,
+              (__nv_bfloat16*)out, inter, total / 8, act);
   else if (dtype == BN_BF16)
     BN_LAUNCH(glu_halves_kernel<__nv_bfloat16>, blocks, 256, 0, stream, (const __nv_bfloat16*)h, (__nv_bfloat16*)out, inter, total, act);
   else

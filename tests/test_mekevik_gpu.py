@@ -203,6 +203,13 @@ def test_the_clamped_unit_and_the_routers_softmax_scores(cuda_device, dtype):
     g, u = np.minimum(h[:, :inter], 1.25), np.clip(h[:, inter:], -1.25, 1.25)
     ref = g * pm.sigmoid(1.702 * g) * (u + 1)
     assert np.abs(out.float().cpu().numpy() - ref).max() < (2e-6 if dtype == "float32" else 2.0 ** -7) * np.abs(ref).max()
+    # the experts' unit on rows of [gate | up], number by number and in 16-byte pieces
+    for inter2 in (21, 24, 200):
+        h2 = bf(rng.standard_normal((n, 2 * inter2)) * 3)
+        out2 = torch.empty((n, inter2), dtype=t, device="cuda")
+        ops.glu_halves(dev(h2, t), out2, ops.ACTIVATIONS["silu"])
+        ref2 = pm.silu(h2[:, :inter2]) * h2[:, inter2:]
+        assert np.abs(out2.float().cpu().numpy() - ref2).max() < (2e-6 if dtype == "float32" else 2.0 ** -7) * np.abs(ref2).max()
     # experts: all of them chosen, one of one, two of five; the weights are the chosen scores over their sum
     for E, top, scale in ((3, 3, 1.5), (1, 1, 2.0), (5, 2, 0.7), (40, 4, 1.0)):
         x, wr = bf(rng.standard_normal((n, 32))), bf(rng.standard_normal((E, 32)))
