@@ -65,6 +65,7 @@ ATT_SHAPES = [  # heads, key/value heads, key width, value width, window, bias b
     (4, 2, 16, 24, 37, 16, 30), (6, 2, 8, 24, 64, 32, 50), (3, 3, 10, 12, 30, 10, 40), (8, 2, 32, 16, 150, 32, 120),
     (5, 1, 6, 7, 0, 20, 100), (2, 2, 64, 32, 1, 6, 20), (16, 4, 64, 64, 129, 32, 300), (4, 1, 128, 128, 65, 8, 70),
     (6, 2, 16, 48, 37, 16, 30), (8, 1, 16, 16, 100, 12, 90), (8, 8, 32, 32, 70, 32, 500), (24, 8, 80, 112, 0, 32, 64), (10, 2, 96, 16, 64, 4, 3),
+    (16, 2, 128, 64, 90, 32, 200), (8, 8, 128, 128, 130, 16, 64), (32, 8, 64, 128, 200, 32, 128), (7, 1, 112, 48, 33, 6, 40),
 ]
 
 
@@ -264,7 +265,7 @@ def _check(got, cfg, w, reqs, plain, dtype, what, rough_ok=False):
     for r, per_pos in sure.items():
         if not per_pos:
             continue
-        gap = np.abs(plain[r] - _plain_rounded(cfg, w, reqs[r])[0]).max(axis=1)
+        gap = np.abs(plain[r] - _plain_rounded(cfg, w, reqs[r])[0]).max(axis=1)[sorted(per_pos)]  # of the positions that are looked at
         bound = BF16_GAP_FACTOR * float(np.percentile(gap, 80))
         if rough_ok and bound >= 0.1 * float(np.abs(plain[r]).max()):
             continue
@@ -407,6 +408,42 @@ def test_models_at_the_edges_of_what_the_configuration_allows(tmp_path, cuda_dev
                             ("an unequal batch", trace_batches([{"a": (reqs["a"], 20), "b": (reqs["b"], 30), "c": (reqs["c"], 0)}]))):
             _check(replay(model, cache, steps), cfg, w, reqs, plain, dtype, f"{kind}, {what}, {dtype}", rough_ok=True)
         model.check_kernels()
+
+
+WIDE = {
+    # heads of 128 numbers; eight query heads on a key/value head, then eight key/value heads with one query head each;
+    # a window that is no multiple of a page
+    "architecture": "Mekevik", "vocab": 1500, "width": 256, "norm": {"eps": 1e-6}, "embedding": {"scale": 4.0}, "logit_scale": 0.5,
+    "layers": [
+        {"type": "attention", "mixer": {"heads": 8, "kv_heads": 1, "dim": 128, "vdim": 64, "scale": 0.09, "bias_max": 100,
+                                        "mask": {"size": 150}, "v_mix": True},
+         "mlp": {"kind": "moe", "router": {"experts": 8, "top": 2, "scale": 2.0}, "expert": {"ff": 48}}},
+        {"type": "attention", "mixer": {"heads": 8, "kv_heads": 8, "dim": 32, "vdim": 8, "scale": 0.18, "bias_max": 300,
+                                        "mask": {"size": 100}, "v_mix": True},
+         "mlp": {"kind": "dense", "ff": 320, "limit": 4.0}},
+        {"type": "attention", "mixer": {"heads": 16, "kv_heads": 4, "dim": 64, "vdim": 128, "scale": 0.125, "bias_max": 64,
+                                        "v_mix": False},
+         "mlp": {"kind": "moe", "router": {"experts": 3, "top": 1, "scale": 1.0}, "expert": {"ff": 200}}},
+    ],
+}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_wider_model_with_heads_of_128_and_eight_heads_either_way(tmp_path, cuda_device, dtype):
+    cfg = WIDE
+    w = mc.draw_weights(cfg, {0: 32, 1: 64, 2: 8}, seed=2)
+    folder = mc.write_folder(str(tmp_path / "m"), cfg, w)
+    V = cfg["vocab"]
+    reqs = {"a": random_tokens(1, 330, V), "b": random_tokens(2, 40, V), "c": random_tokens(3, 17, V)}
+    plain = {r: pm.forward(cfg, w, t) for r, t in reqs.items()}
+    model = bn.load_model(folder, dtype=dtype)
+    cache = model.new_cache(max_tokens=64 * 12, max_seqs=3)
+    _poison(cache)
+    for what, steps in (("whole", trace_whole(reqs)), ("last 40 one by one", trace_tail(reqs, 40)),
+                        ("pieces", trace_chunks(reqs, pieces=(16, 1, 100, 3))),
+                        ("an unequal batch", trace_batches([{"a": (reqs["a"], 30), "b": (reqs["b"], 30), "c": (reqs["c"], 5)}]))):
+        _check(replay(model, cache, steps), cfg, w, reqs, plain, dtype, f"wide, {what}, {dtype}")
+    model.check_kernels()
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
