@@ -42,6 +42,11 @@ __device__ __forceinline__ float4 sp_ld4(unsigned cluster_addr) {
   asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(cluster_addr));
   return v;
 }
+__device__ __forceinline__ float sp_ld1(unsigned cluster_addr) {
+  float v;
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(cluster_addr));
+  return v;
+}
 __device__ __forceinline__ float sp_rest(float p) { return p - __bfloat162float(__float2bfloat16_rn(p)); }
 
 struct SpArgs {
@@ -65,7 +70,12 @@ struct SpArgs {
 
 // RP: the query heads per key/value head, rounded up to a power of two (the mixing keeps so many accumulators
 // per column); the warps per query head follow from it, so that a block has about eight warps.
-template <int HD, int VD, int RP>
+// SLICE (4 or 8 key/value heads, up to 4 query heads each): the mixing is dealt out by keys instead.  Block c
+// reads all heads' weights of its 64 / G keys only, mixes them for *all* heads, and leaves the mixed weights in its
+// shared memory, from where every block fetches its own heads' (a second cluster barrier in between): every weight
+// crosses the SM-to-SM network about twice instead of once per block of the cluster.  The values have one
+// stage then (asked for at the top of their page's turn, needed at its end).
+template <int HD, int VD, int RP, bool SLICE>
 __global__ void __launch_bounds__(32 * SP_MAX_R, RP <= 4 ? 2 : 1)
 sigmoid_attention_prefill_kernel(const SpArgs a) {
   constexpr int WPH = RP <= 2 ? 4 : (RP <= 4 ? 2 : 1);
@@ -83,12 +93,17 @@ sigmoid_attention_prefill_kernel(const SpArgs a) {
   const int c = blockIdx.x;  // key/value head = rank in the cluster
   const int h = c * R + hr;
   const unsigned s_k = (unsigned)__cvta_generic_to_shared(smem);   // two stages
-  const unsigned s_v = s_k + 2 * KTILE;                            // two stages
-  float* s_a = reinterpret_cast<float*>(smem + 2 * KTILE + 2 * VTILE);  // [R][16][SP_LD] this block's heads' weights
+  const unsigned s_v = s_k + 2 * KTILE;                            // two stages (SLICE: one)
+  constexpr int V_STAGES = SLICE ? 1 : 2;
+  const int G = a.n_kv_heads;
+  float* s_a = reinterpret_cast<float*>(smem + 2 * KTILE + V_STAGES * VTILE);  // [R][16][SP_LD] this block's heads' weights
   float* s_w = s_a + R * SP_M * SP_LD;                                  // [R][16][SP_LD] the same heads' mixed weights
-  float* s_mix = s_w + R * SP_M * SP_LD;                                // [H][SP_MAX_R]: mix[c * R + r][g] at [g][r]
-  float* s_bias = s_mix + H * SP_MAX_R;                                 // [warps][SP_BIAS]
+  // [H][SP_MAX_R]: mix[c * R + r][g] at [g][r]; SLICE: [H][G][SP_MAX_R]: mix[c2 * R + r][g] at [g][c2][r]
+  float* s_mix = s_w + R * SP_M * SP_LD;
+  float* s_bias = s_mix + H * SP_MAX_R * (SLICE ? G : 1);               // [warps][SP_BIAS]
+  float* s_ws = s_bias + n_warps * SP_BIAS;                             // SLICE: [H][16][64 / G] all heads' mixed weights of this block's keys
   const unsigned s_a_addr = (unsigned)__cvta_generic_to_shared(s_a);
+  const unsigned s_ws_addr = (unsigned)__cvta_generic_to_shared(s_ws);
 
   const int blk = gridDim.y - 1 - blockIdx.y;
   const int seq = a.tile_seq[blk], row0 = (a.tile_row0 ? a.tile_row0[blk] : 0) + (a.part ? 0 : blockIdx.z * SP_M);
@@ -115,9 +130,9 @@ sigmoid_attention_prefill_kernel(const SpArgs a) {
     }
     cp_async_commit();
   }
-  for (int i = tid; i < H * SP_MAX_R; i += n_threads) {
-    const int g = i / SP_MAX_R, r = i % SP_MAX_R;
-    s_mix[i] = r < R ? (a.mix ? a.mix[(size_t)(c * R + r) * H + g] : (g == c * R + r ? 1.f : 0.f)) : 0.f;
+  for (int i = tid; i < H * SP_MAX_R * (SLICE ? G : 1); i += n_threads) {
+    const int r = i % SP_MAX_R, c2 = SLICE ? (i / SP_MAX_R) % G : c, g = i / (SP_MAX_R * (SLICE ? G : 1));
+    s_mix[i] = r < R ? (a.mix ? a.mix[(size_t)(c2 * R + r) * H + g] : (g == c2 * R + r ? 1.f : 0.f)) : 0.f;
   }
   cp_async_wait<0>();
   __syncthreads();
@@ -132,14 +147,16 @@ sigmoid_attention_prefill_kernel(const SpArgs a) {
 
   // the page's number is asked for one page ahead of its rows, the bias of a page's distances one page ahead of
   // its scores: no warp waits for either
-  auto load_kv = [&](int tile, int page, int stage) {
+  auto load_k = [&](int page, int stage) {
     const __nv_bfloat16* kb = a.k_cache + ((size_t)page * a.n_kv_heads + c) * BN_PAGE * a.head_dim;
-    const __nv_bfloat16* vb = a.v_cache + ((size_t)page * a.n_kv_heads + c) * BN_PAGE * a.v_dim;
     for (int p = tid; p < SP_N * CHUNKS; p += n_threads) {
       const int r = p / CHUNKS, ch = p % CHUNKS;
       const bool ok = ch < real_chunks;
       cp_async16(s_k + stage * KTILE + sp_off<HD>(r, ch), ok ? kb + (size_t)r * a.head_dim + ch * 8 : kb, ok);
     }
+  };
+  auto load_v = [&](int tile, int page, int stage) {
+    const __nv_bfloat16* vb = a.v_cache + ((size_t)page * a.n_kv_heads + c) * BN_PAGE * a.v_dim;
     for (int p = tid; p < SP_N * VCHUNKS; p += n_threads) {
       const int r = p / VCHUNKS, ch = p % VCHUNKS;
       // rows behind the sequence's last position are zero, whatever the cache holds: zero weights times anything stay zero
@@ -147,7 +164,11 @@ sigmoid_attention_prefill_kernel(const SpArgs a) {
       cp_async16(s_v + stage * VTILE + sp_off<VD>(r, ch), ok ? vb + (size_t)r * a.v_dim + ch * 8 : vb, ok);
     }
   };
-  if (n_walk > 0) load_kv(tile_lo, pt[tile_lo], 0);
+  int page_cur = n_walk > 0 ? pt[tile_lo] : 0;
+  if (n_walk > 0) {
+    load_k(page_cur, 0);
+    if (!SLICE) load_v(tile_lo, page_cur, 0);
+  }
   cp_async_commit();
   int page_next = n_walk > 1 ? pt[tile_lo + stride] : 0;
   auto bias_of = [&](int tile, int x) {  // of distance (q_first - the tile's last key) + lane + 32 x, for this warp's head
@@ -178,11 +199,14 @@ sigmoid_attention_prefill_kernel(const SpArgs a) {
     const int tile = tile_lo + u * stride, stage = u & 1;
     cp_async_wait<0>();
     __syncthreads();  // this page is here; everybody is done with the other stage and with the mixed weights
+    if (SLICE) load_v(tile, page_cur, 0);  // everybody is done with the page before
     if (u + 1 < n_walk) {
-      load_kv(tile + stride, page_next, stage ^ 1);
-      cp_async_commit();
+      load_k(page_next, stage ^ 1);
+      if (!SLICE) load_v(tile + stride, page_next, stage ^ 1);
+      page_cur = page_next;
       if (u + 2 < n_walk) page_next = pt[tile + 2 * stride];
     }
+    cp_async_commit();
     const int dist0 = q_first - (tile * SP_N + SP_N - 1);
     if (a.rel) {
 #pragma unroll
@@ -198,7 +222,7 @@ sigmoid_attention_prefill_kernel(const SpArgs a) {
     float s[NJ][4];
 #pragma unroll
     for (int j = 0; j < NJ; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
-    const unsigned kb = s_k + stage * KTILE, vb = s_v + stage * VTILE;
+    const unsigned kb = s_k + stage * KTILE, vb = s_v + (SLICE ? 0 : stage * VTILE);
 #pragma unroll
     for (int ks = 0; ks < KSTEPS; ++ks) {
 #pragma unroll
@@ -210,7 +234,7 @@ sigmoid_attention_prefill_kernel(const SpArgs a) {
         mma_bf16(s[j + 1], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], b2, b3);
       }
     }
-    if (u > 0) sp_cluster_wait();  // every block has read the weights of the page before
+    if (!SLICE && u > 0) sp_cluster_wait();  // every block has read the weights of the page before
     const int kbase = tile * SP_N;
 #pragma unroll
     for (int j = 0; j < NJ; ++j) {
@@ -231,8 +255,54 @@ sigmoid_attention_prefill_kernel(const SpArgs a) {
     sp_cluster_arrive();
     sp_cluster_wait();  // all heads' weights of this page are written
     // ---- mixing: this warp's column groups, all heads in, this block's heads out
+    if (SLICE) {
+      // ---- mixing by keys: this block's 64 / G keys, all heads in, all heads out, four blocks' heads at a time
+      const int KS = SP_N / G, P = SP_M * KS, n_dg = (G + 3) / 4;
+      for (int it = tid; it < P * n_dg; it += n_threads) {
+        const int pair = it % P, dg = it / P, row = pair / KS, k = pair % KS;
+        float acc[4][RP];
+#pragma unroll
+        for (int d = 0; d < 4; ++d)
+#pragma unroll
+          for (int r = 0; r < RP; ++r) acc[d][r] = 0.f;
+        const unsigned at = (unsigned)((row * SP_LD + c * KS + k) * 4);
+        for (int cg = 0; cg < G; ++cg) {
+          const unsigned base = sp_map(s_a_addr, (unsigned)cg) + at;
+          float v[4];
+#pragma unroll
+          for (int x = 0; x < 4; ++x) v[x] = sp_ld1(base + (unsigned)(min(x, R - 1) * SP_M * SP_LD * 4));
+#pragma unroll
+          for (int x = 0; x < 4; ++x) {
+            if (x < R) {
+              const float* mrow = s_mix + ((cg * R + x) * G + dg * 4) * SP_MAX_R;  // the factors of heads beyond R are zeros
+#pragma unroll
+              for (int d = 0; d < 4; ++d) {
+                float m[4];
+                *reinterpret_cast<float4*>(m) = *reinterpret_cast<const float4*>(mrow + d * SP_MAX_R);
+#pragma unroll
+                for (int r = 0; r < RP; ++r) acc[d][r] = fmaf(m[r], v[x], acc[d][r]);
+              }
+            }
+          }
+        }
+#pragma unroll
+        for (int d = 0; d < 4; ++d)
+#pragma unroll
+          for (int r = 0; r < RP; ++r)
+            if (dg * 4 + d < G && r < R) s_ws[(((dg * 4 + d) * R + r) * SP_M + row) * KS + k] = acc[d][r];
+      }
+      sp_cluster_arrive();
+      sp_cluster_wait();  // all blocks' mixed weights of this page are written
+      // ---- this block's heads' mixed weights of all keys, 16 bytes at a time
+      for (int idx = tid; idx < R * SP_M * (SP_N / 4); idx += n_threads) {
+        const int r = idx / (SP_M * (SP_N / 4)), rem = idx % (SP_M * (SP_N / 4)), row = rem / (SP_N / 4), key0 = (rem % (SP_N / 4)) * 4;
+        const float4 v = sp_ld4(sp_map(s_ws_addr, (unsigned)(key0 / KS)) + (unsigned)(((((c * R + r) * SP_M + row) * KS) + key0 % KS) * 4));
+        *reinterpret_cast<float4*>(s_w + (r * SP_M + row) * SP_LD + key0) = v;
+      }
+      cp_async_wait<0>();  // this page's values (and the next page's keys) are here
+    }
     // a lane takes four neighbouring keys of one row: a 16 x 8 group of a head is one 16-byte read per lane
-    for (int j = warp; j < SP_N / 8; j += n_warps) {
+    for (int j = SLICE ? SP_N : warp; j < SP_N / 8; j += n_warps) {
       float acc[RP][4];
 #pragma unroll
       for (int r = 0; r < RP; ++r) acc[r][0] = acc[r][1] = acc[r][2] = acc[r][3] = 0.f;
@@ -268,8 +338,8 @@ sigmoid_attention_prefill_kernel(const SpArgs a) {
       for (int r = 0; r < RP; ++r)
         if (r < R) *reinterpret_cast<float4*>(s_w + r * SP_M * SP_LD + at_f) = make_float4(acc[r][0], acc[r][1], acc[r][2], acc[r][3]);
     }
-    sp_cluster_arrive();  // this block reads no other's weights of this page any more
-    __syncthreads();      // the mixed weights of all column groups are written
+    if (!SLICE) sp_cluster_arrive();  // this block reads no other's weights of this page any more
+    __syncthreads();                  // the mixed weights of all column groups are written
     // ---- O += W V, the weights as two bfloat16 terms
 #pragma unroll
     for (int ks = 0; ks < SP_N / 16; ++ks) {
@@ -292,6 +362,7 @@ sigmoid_attention_prefill_kernel(const SpArgs a) {
       }
     }
   }
+  if (SLICE && n_walk > 0) sp_cluster_arrive();
   if (n_walk > 0) sp_cluster_wait();  // no block leaves while another still reads its weights
   if (a.part) {
 #pragma unroll
@@ -352,26 +423,32 @@ __global__ void sigmoid_attention_sum_kernel(const float* __restrict__ part, int
 // Warps per query head: so that a block has about eight warps (the kernel's WPH).
 static int sp_wph(int R) { return R <= 2 ? 4 : (R <= 4 ? 2 : 1); }
 
-static size_t sp_smem_bytes(int hd, int vd, int n_heads, int R) {
-  return 2 * (size_t)SP_N * hd * 2 + 2 * (size_t)SP_N * vd * 2 +
-         ((size_t)2 * R * SP_M * SP_LD + (size_t)n_heads * SP_MAX_R + (size_t)R * sp_wph(R) * SP_BIAS) * sizeof(float);
+// The mixing is dealt out by keys (the kernel's SLICE) where that moves fewer bytes between the blocks.
+static bool sp_slice(int n_kv_heads, int R) { return (n_kv_heads == 4 || n_kv_heads == 8) && R <= 4; }
+
+static size_t sp_smem_bytes(int hd, int vd, int n_heads, int n_kv_heads) {
+  const int R = n_heads / n_kv_heads;
+  const bool slice = sp_slice(n_kv_heads, R);
+  return 2 * (size_t)SP_N * hd * 2 + (slice ? 1 : 2) * (size_t)SP_N * vd * 2 +
+         ((size_t)2 * R * SP_M * SP_LD + (size_t)n_heads * SP_MAX_R * (slice ? n_kv_heads : 1) + (size_t)R * sp_wph(R) * SP_BIAS +
+          (slice ? (size_t)n_heads * SP_M * (SP_N / n_kv_heads) : 0)) * sizeof(float);
 }
 
-template <int HD, int VD, int RP>
+template <int HD, int VD, int RP, bool SLICE>
 static int sp_launch_w(const SpArgs& a, int n_tiles, cudaStream_t stream) {
   const int WPH = sp_wph(RP);
   const int R = a.n_heads / a.n_kv_heads;
-  const size_t smem = sp_smem_bytes(HD, VD, a.n_heads, R);
+  const size_t smem = sp_smem_bytes(HD, VD, a.n_heads, a.n_kv_heads);
   static size_t granted = 0;
   if (smem > granted) {
-    cudaError_t e = cudaFuncSetAttribute(sigmoid_attention_prefill_kernel<HD, VD, RP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(sigmoid_attention_prefill_kernel<HD, VD, RP, SLICE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return BN_ERR_LAUNCH + (int)e;
     granted = smem;
   }
   // one cluster per 16 rows: the blocks of 64 rows of the step's list, four deep; or, with the pages dealt out,
   // one cluster per block of (at most 16) rows and share of the pages
   dim3 grid(a.n_kv_heads, n_tiles, a.part ? a.n_splits : 64 / SP_M);
-  cudaError_t e = bn_launch_cluster(sigmoid_attention_prefill_kernel<HD, VD, RP>, grid, dim3(32 * R * WPH), smem, stream,
+  cudaError_t e = bn_launch_cluster(sigmoid_attention_prefill_kernel<HD, VD, RP, SLICE>, grid, dim3(32 * R * WPH), smem, stream,
                                     dim3(a.n_kv_heads, 1, 1), a);
   if (e != cudaSuccess) return BN_ERR_LAUNCH + (int)e;
   BN_CHECK_LAUNCH();
@@ -381,10 +458,15 @@ static int sp_launch_w(const SpArgs& a, int n_tiles, cudaStream_t stream) {
 template <int HD, int VD>
 static int sp_launch(const SpArgs& a, int n_tiles, cudaStream_t stream) {
   const int R = a.n_heads / a.n_kv_heads;
-  if (R == 1) return sp_launch_w<HD, VD, 1>(a, n_tiles, stream);
-  if (R == 2) return sp_launch_w<HD, VD, 2>(a, n_tiles, stream);
-  if (R <= 4) return sp_launch_w<HD, VD, 4>(a, n_tiles, stream);
-  return sp_launch_w<HD, VD, 8>(a, n_tiles, stream);
+  if (sp_slice(a.n_kv_heads, R)) {
+    if (R == 1) return sp_launch_w<HD, VD, 1, true>(a, n_tiles, stream);
+    if (R == 2) return sp_launch_w<HD, VD, 2, true>(a, n_tiles, stream);
+    return sp_launch_w<HD, VD, 4, true>(a, n_tiles, stream);
+  }
+  if (R == 1) return sp_launch_w<HD, VD, 1, false>(a, n_tiles, stream);
+  if (R == 2) return sp_launch_w<HD, VD, 2, false>(a, n_tiles, stream);
+  if (R <= 4) return sp_launch_w<HD, VD, 4, false>(a, n_tiles, stream);
+  return sp_launch_w<HD, VD, 8, false>(a, n_tiles, stream);
 }
 
 // Whether the sizes fit this kernel (1) or want the general one (0): bfloat16 rows in whole 16-element steps up
@@ -393,7 +475,7 @@ static int sp_launch(const SpArgs& a, int n_tiles, cudaStream_t stream) {
 extern "C" int bn_sigmoid_attention_prefill_fits(int n_heads, int n_kv_heads, int head_dim, int v_dim) {
   if (n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads || n_kv_heads > 8 || n_heads / n_kv_heads > SP_MAX_R) return 0;
   if (head_dim <= 0 || head_dim % 16 || head_dim > 128 || v_dim <= 0 || v_dim % 16 || v_dim > 128) return 0;
-  return sp_smem_bytes(head_dim <= 64 ? 64 : 128, v_dim <= 64 ? 64 : 128, n_heads, n_heads / n_kv_heads) <= 200 * 1024;
+  return sp_smem_bytes(head_dim <= 64 ? 64 : 128, v_dim <= 64 ? 64 : 128, n_heads, n_kv_heads) <= 200 * 1024;
 }
 
 // q: [tokens, q_stride] bfloat16 (head h at element h * head_dim), out [tokens, out_stride] (head h at element
