@@ -16,6 +16,9 @@
 // of two bfloat16 terms (16 bits of mantissa), accumulating in float32 registers over all pages.  The second
 // cluster barrier of a page (no block overwrites weights another still reads) is split: arrive after the
 // mixing, wait before the next page's weights are written.
+// With four or eight key/value heads of up to four query heads each the exchange runs the other way (SLICE below):
+// a block mixes all heads' weights of its share of the page's keys, and every block then fetches its own heads'
+// mixed weights, which moves a fraction of the bytes between the blocks.
 // The new tokens' keys and values must already be in the cache; pages are [page][kv head][64][width].
 #include "mma.cuh"
 

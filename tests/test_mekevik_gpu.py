@@ -18,6 +18,17 @@ from helpers import (BF16_GAP_FACTOR, TOL_F32, collect_trace_output, compare, ra
                      trace_batches, trace_chunks, trace_tail, trace_whole)
 
 pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module", autouse=True)
+def _give_device_memory_back():
+    """The models and caches of this module leave the allocator's pool when it is done."""
+    yield
+    import gc
+    import torch as _torch
+    gc.collect()
+    if _torch.cuda.is_available():
+        _torch.cuda.empty_cache()
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
 bf = pm.to_bf16

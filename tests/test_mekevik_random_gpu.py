@@ -15,6 +15,17 @@ from test_mekevik_gpu import _check, _poison
 pytestmark = pytest.mark.gpu
 
 
+@pytest.fixture(scope="module", autouse=True)
+def _give_device_memory_back():
+    """The models and caches of this module leave the allocator's pool when it is done."""
+    yield
+    import gc
+    import torch as _torch
+    gc.collect()
+    if _torch.cuda.is_available():
+        _torch.cuda.empty_cache()
+
+
 def draw_config(seed: int):
     rng = np.random.default_rng(seed)
     pick = lambda xs: xs[int(rng.integers(len(xs)))]
