@@ -77,6 +77,7 @@ ATT_SHAPES = [  # heads, key/value heads, key width, value width, window, bias b
     (5, 1, 6, 7, 0, 20, 100), (2, 2, 64, 32, 1, 6, 20), (16, 4, 64, 64, 129, 32, 300), (4, 1, 128, 128, 65, 8, 70),
     (6, 2, 16, 48, 37, 16, 30), (8, 1, 16, 16, 100, 12, 90), (8, 8, 32, 32, 70, 32, 500), (24, 8, 80, 112, 0, 32, 64), (10, 2, 96, 16, 64, 4, 3),
     (16, 2, 128, 64, 90, 32, 200), (8, 8, 128, 128, 130, 16, 64), (32, 8, 64, 128, 200, 32, 128), (7, 1, 112, 48, 33, 6, 40),
+    (8, 4, 32, 64, 77, 16, 100), (16, 8, 16, 16, 140, 32, 90), (12, 4, 48, 32, 0, 8, 30), (4, 4, 64, 16, 64, 32, 64),
 ]
 
 
