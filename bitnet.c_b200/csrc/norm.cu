@@ -298,6 +298,58 @@ extern "C" int bn_residual_add(float* x, const void* a, int a_dtype, const void*
   return BN_OK;
 }
 
+// x += a (+ b) as above, then the norms that read the stream next, in the same pass: out1 = x * rsqrt(mean(x^2) + eps) * w1
+// and, if w2 is given, out2 = the same rows times w2 (two norms of one stream share their statistics).  One block
+// per row; float32 sums and statistics; out1 / out2 in the compute type.
+__global__ void residual_add_norms_kernel(float* __restrict__ x, const void* __restrict__ a, int a_dtype, const void* __restrict__ b,
+                                          int b_dtype, const void* __restrict__ w1, const void* __restrict__ w2, int w_dtype,
+                                          float eps, void* __restrict__ out1, void* __restrict__ out2, int out_dtype, int width) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ __align__(16) float v[];  // width floats, then 32 for the reduction
+  float* scratch = v + width;
+  const size_t row = blockIdx.x;
+  float* xr = x + row * width;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    float d = load_as_f32(a, a_dtype, row * width + i);
+    if (b) d += load_as_f32(b, b_dtype, row * width + i);  // the sublayers' sum first, then onto the stream
+    const float t = xr[i] + d;
+    xr[i] = t;
+    v[i] = t;
+    ss += t * t;
+  }
+  ss = block_sum(ss, scratch);
+  const float scale = 1.0f / sqrtf(ss / (float)width + eps);
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    const float t = v[i] * scale;
+    store_from_f32(out1, out_dtype, row * width + i, t * load_as_f32(w1, w_dtype, i));
+    if (w2) store_from_f32(out2, out_dtype, row * width + i, t * load_as_f32(w2, w_dtype, i));
+  }
+}
+
+extern "C" int bn_residual_add_norms(float* x, const void* a, int a_dtype, const void* b, int b_dtype, const void* w1, const void* w2,
+                                     int w_dtype, float eps, void* out1, void* out2, int out_dtype, int n_rows, int width,
+                                     cudaStream_t stream) {
+  if (n_rows <= 0) return BN_OK;
+  if (width <= 0 || !(eps > 0.f) || !x || !a || !w1 || !out1 || (w2 && !out2)) return BN_ERR_BAD_ARG;
+  size_t smem = ((size_t)width + 32) * sizeof(float);
+  if (smem > 200 * 1024) return BN_ERR_BAD_ARG;
+  if (smem > 48 * 1024) {
+    static size_t granted = 0;
+    if (smem > granted) {
+      cudaError_t e = cudaFuncSetAttribute(residual_add_norms_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return BN_ERR_LAUNCH + (int)e;
+      granted = smem;
+    }
+  }
+  int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
+  BN_LAUNCH(residual_add_norms_kernel, n_rows, threads, smem, stream, x, a, a_dtype, b, b_dtype, w1, w2, w_dtype, eps, out1, out2,
+            out_dtype, width);
+  BN_CHECK_LAUNCH();
+  return BN_OK;
+}
+
 // x += y / sqrt(mean(y^2) + eps_y) * wy: a delta that enters the stream through a norm of its own.
 // Then, if `w` is given, out[r] = x * rsqrt(mean(x^2) + eps) * w: the norm that reads the stream next,
 // in the same pass (out in the compute type).  One block per row; float32 statistics.

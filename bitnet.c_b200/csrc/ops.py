@@ -1320,6 +1320,30 @@ def residual_add(x: torch.Tensor, a: torch.Tensor, b: Optional[torch.Tensor] = N
     return x if cast == torch.float32 else out
 
 
+RESIDUAL_NORMS_MAX_WIDTH = (200 * 1024) // 4 - 32  # rows that fit the fused kernel's shared memory
+
+
+def residual_add_norms(x: torch.Tensor, a: torch.Tensor, b: Optional[torch.Tensor], w1: torch.Tensor, w2: Optional[torch.Tensor],
+                       eps: float, out_dtype: torch.dtype):
+    """x += a (+ b) on the float32 residual (the two deltas are added to each other first), and in the same pass
+    the norms that read the new rows next: ``(x / rms(x) * w1, x / rms(x) * w2 or None)`` in ``out_dtype``."""
+    _need(x, "x", torch.float32, 2)
+    _need(a, "a", dims=2)
+    _need(w1, "w1", dims=1)
+    if a.shape != x.shape or (b is not None and (b.shape != x.shape or not b.is_cuda)) or w1.shape[0] != x.shape[1]:
+        raise KernelError("residual_add_norms: sizes do not fit")
+    if w2 is not None:
+        _need(w2, "w2", w1.dtype, 1)
+        if w2.shape[0] != x.shape[1]:
+            raise KernelError("residual_add_norms: the second gain does not fit")
+    out1 = torch.empty(x.shape, dtype=out_dtype, device=x.device)
+    out2 = torch.empty(x.shape, dtype=out_dtype, device=x.device) if w2 is not None else None
+    _check(_fn("norm", "bn_residual_add_norms")(_ptr(x), _ptr(a), int(_code(a)), _ptr(b), int(_code(b)) if b is not None else 0,
+                                                _ptr(w1), _ptr(w2), int(_code(w1)), c_float(eps), _ptr(out1), _ptr(out2),
+                                                int(_code(out1)), int(x.shape[0]), int(x.shape[1]), _stream()), "residual_add_norms")
+    return out1, out2
+
+
 def add_normed(x: torch.Tensor, y: torch.Tensor, wy: torch.Tensor, eps_y: float, w: Optional[torch.Tensor] = None,
                eps: float = 0.0, out_dtype: Optional[torch.dtype] = None) -> Optional[torch.Tensor]:
     """x += y / sqrt(mean(y^2) + eps_y) * wy on the float32 residual; with ``w`` also returns

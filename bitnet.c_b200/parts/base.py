@@ -151,8 +151,9 @@ class Normed:
     """A norm's output that an earlier product already prepared in its epilogue (``value`` is a
     tensor or ``ops.RowScaled``); a block that gets it as ``pending`` skips its first norm."""
 
-    def __init__(self, value):
+    def __init__(self, value, second=None):
         self.value = value
+        self.second = second  # the same rows under the reader's second norm, where it has one (``norm.sibling``)
 
 
 class Cast:

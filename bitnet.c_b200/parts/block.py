@@ -134,6 +134,8 @@ class ParallelBlock(Block):
         self.side = build_part("side", spec.side, build) if spec.side is not None else None
         ffn_norm = getattr(spec, "ffn_norm", None)
         self.ffn_norm = build_part("norm", ffn_norm, build) if ffn_norm is not None else None
+        if self.ffn is not None and self.ffn_norm is not None:
+            self.norm.sibling = self.ffn_norm  # who prepares this block's first norm can prepare its second in the same pass
 
     def children(self):
         c = {"norm": self.norm, "mixer": self.mixer}
@@ -162,7 +164,9 @@ class ParallelBlock(Block):
         ctx.tap("attn_norm", h)
         h2 = h
         if self.ffn is not None and self.ffn_norm is not None:
-            h2 = self.ffn_norm.add_norm(x, None, ctx)  # the second norm of the same rows (the delta is in them by now)
+            h2 = pending.second if isinstance(pending, Normed) and pending.second is not None else None
+            if h2 is None:
+                h2 = self.ffn_norm.add_norm(x, None, ctx)  # the second norm of the same rows (the delta is in them by now)
             ctx.tap("ffn_norm", h2)
         d = self.mixer.forward(h, ctx, kv, state)
         ctx.tap("attn_proj", d)
@@ -170,8 +174,17 @@ class ParallelBlock(Block):
         if f is not None:
             ctx.tap("ffn_out", f)
         if self.side is None:
-            ops.residual_add(x, d, f)
-            return None
+            w1 = getattr(next_norm, "weight", None) if next_norm is not None else None
+            if w1 is None or x.shape[1] > ops.RESIDUAL_NORMS_MAX_WIDTH:
+                ops.residual_add(x, d, f)
+                return None
+            # the sum of the deltas and the norms that read the stream next (the next block's, both of them where
+            # it has two: they share their statistics) in one pass
+            sib = getattr(next_norm, "sibling", None)
+            w2 = getattr(sib, "weight", None) if sib is not None and sib.spec.eps == next_norm.spec.eps else None
+            h1, h2n = ops.residual_add_norms(x, d, f, w1, w2.to(w1.dtype) if w2 is not None and w2.dtype != w1.dtype else w2,
+                                             next_norm.spec.eps, self.build.dtype)
+            return Normed(h1, second=h2n)
         xc = ops.residual_add(x, d, f, cast=self.build.dtype)
         y = self.side.delta(xc, ctx)
         ctx.tap("side_out", y)

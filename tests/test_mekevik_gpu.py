@@ -233,6 +233,27 @@ def test_the_clamped_unit_and_the_routers_softmax_scores(cuda_device, dtype):
         assert np.abs(np.take_along_axis(wts.cpu().numpy(), order_g, 1) - np.take_along_axis(want_w, order_w, 1)).max() < 1e-5 * scale
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("width", [50, 192, 1030])
+def test_the_sum_of_the_deltas_and_the_next_blocks_two_norms_in_one_pass(cuda_device, dtype, width):
+    from bitnet_c_b200.csrc import ops
+    rng = np.random.default_rng(width)
+    t = DT[dtype]
+    n = 7
+    x, a, b = rng.standard_normal((n, width)) * 2, bf(rng.standard_normal((n, width))), rng.standard_normal((n, width))
+    w1, w2 = bf(1 + 0.3 * rng.standard_normal(width)), bf(1 + 0.3 * rng.standard_normal(width))
+    tol = 2e-6 if dtype == "float32" else 2.0 ** -7
+    for second, with_b in ((True, True), (False, True), (True, False)):
+        xd = dev(x)
+        h1, h2 = ops.residual_add_norms(xd, dev(a, t), dev(b) if with_b else None, dev(w1, t), dev(w2, t) if second else None, 1e-5, t)
+        want = x.astype(np.float32).astype(np.float64) + (a + (b.astype(np.float32) if with_b else 0.0))
+        assert np.abs(xd.cpu().numpy() - want).max() < 1e-6 * np.abs(want).max()
+        assert np.abs(h1.float().cpu().numpy() - pm.rms_norm(want, w1, 1e-5)).max() < tol * 4
+        assert (h2 is None) == (not second)
+        if second:
+            assert np.abs(h2.float().cpu().numpy() - pm.rms_norm(want, w2, 1e-5)).max() < tol * 4
+
+
 # ---- whole models ------------------------------------------------------------------------------------
 @pytest.fixture(scope="module")
 def folders(tmp_path_factory):
