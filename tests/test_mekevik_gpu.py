@@ -78,6 +78,7 @@ ATT_SHAPES = [  # heads, key/value heads, key width, value width, window, bias b
     (6, 2, 16, 48, 37, 16, 30), (8, 1, 16, 16, 100, 12, 90), (8, 8, 32, 32, 70, 32, 500), (24, 8, 80, 112, 0, 32, 64), (10, 2, 96, 16, 64, 4, 3),
     (16, 2, 128, 64, 90, 32, 200), (8, 8, 128, 128, 130, 16, 64), (32, 8, 64, 128, 200, 32, 128), (7, 1, 112, 48, 33, 6, 40),
     (8, 4, 32, 64, 77, 16, 100), (16, 8, 16, 16, 140, 32, 90), (12, 4, 48, 32, 0, 8, 30), (4, 4, 64, 16, 64, 32, 64),
+    (6, 3, 16, 16, 50, 8, 40), (5, 5, 32, 16, 20, 8, 40), (12, 6, 16, 32, 90, 16, 70), (7, 7, 16, 16, 33, 6, 40),  # clusters of 3, 5, 6, 7 blocks
 ]
 
 
