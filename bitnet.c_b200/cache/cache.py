@@ -5,7 +5,8 @@ the *group* of all entries with the same request (heads, head size, window).  A 
 own storage, page pool and page table, so runs with different needs never share memory:
 
     k             [entries, pages, kv_heads, 64, head_dim]   compute type
-    v             [entries, pages, kv_heads, 64, v_head_dim] (a value head may be narrower or wider than a key head)
+    v             [entries, pages, kv_heads, 64, v_head_dim] (a value head may be narrower or wider than a key head,
+                  and there may be fewer value heads than key heads when several key heads read one)
     page_table    [slots, pages_per_sequence]  int32, on the device and mirrored on the host
 
 A sequence lives in a *slot* from its first token to its end and holds, in each group, the
@@ -36,7 +37,7 @@ class KvView:
     """What a mixer sees of the cache for one run."""
 
     k: torch.Tensor  # [pages, kv_heads, PAGE, head_dim]
-    v: Optional[torch.Tensor]  # [pages, kv_heads, PAGE, v_head_dim]; None: the values are a part of the key rows
+    v: Optional[torch.Tensor]  # [pages, value heads, PAGE, v_head_dim]; None: the values are a part of the key rows
     page_table: torch.Tensor  # [slots, pages_per_sequence] int32
     n_kv_heads: int
     head_dim: int
@@ -82,14 +83,16 @@ class KvGroup:
         shape = (len(entries), n_pages, request.n_kv_heads, PAGE, request.head_dim)
         if allocate:
             self.k = torch.zeros(shape, dtype=dtype, device=device)
-            self.v = None if request.values_in_keys else torch.zeros(shape[:-1] + (request.v_dim,), dtype=dtype, device=device)
+            self.v = None if request.values_in_keys else torch.zeros(shape[:2] + (request.n_v_heads, PAGE, request.v_dim),
+                                                                      dtype=dtype, device=device)
             self.page_table = torch.zeros((n_slots, pages_per_seq), dtype=torch.int32, device=device)
         else:  # bookkeeping only (tests without a device)
             self.k = self.v = self.page_table = None
 
     def bytes_per_token(self, itemsize: int) -> int:
-        per_head = self.request.head_dim + (0 if self.request.values_in_keys else self.request.v_dim)
-        return len(self.entries) * self.request.n_kv_heads * per_head * itemsize
+        r = self.request
+        per_token = r.n_kv_heads * r.head_dim + (0 if r.values_in_keys else r.n_v_heads * r.v_dim)
+        return len(self.entries) * per_token * itemsize
 
     def reserve(self, slot: int, old_len: int, new_len: int) -> None:
         """Hold pages for positions [first needed, new_len)."""
@@ -189,7 +192,7 @@ class Cache:
             if src not in self._plane:
                 raise CacheError(f"schedule entry {i} reads the cache of entry {src}, which has none")
             a, b = kv_requests[i], kv_requests[src]
-            if a is not None and (a.n_kv_heads, a.head_dim, a.v_dim) != (b.n_kv_heads, b.head_dim, b.v_dim):
+            if a is not None and (a.n_kv_heads, a.head_dim, a.v_dim, a.n_v_heads) != (b.n_kv_heads, b.head_dim, b.v_dim, b.n_v_heads):
                 raise CacheError(f"schedule entry {i} cannot read entry {src}'s cache: "
                                  f"{a.n_kv_heads}x{a.head_dim}/{a.v_dim} against {b.n_kv_heads}x{b.head_dim}/{b.v_dim}")
             self._reader[i] = src

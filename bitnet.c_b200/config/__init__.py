@@ -2,6 +2,7 @@
 from .spec import (BiasAttentionSpec, MlstmSpec, MoeSpec, PostNormBlockSpec)  # noqa: F401
 from .spec import (DeltaRuleSpec, LatentAttentionSpec, ParallelBlockSpec, RotaryPairsSpec, TokenSideSpec)  # noqa: F401
 from .spec import (LimitedMlpSpec, SigmoidAttentionSpec)  # noqa: F401
+from .spec import (NormedAttentionSpec, RotaryBlendSpec, SandwichBlockSpec)  # noqa: F401
 from .spec import (AttentionSpec, BlockSpec, ConfigError, GatedMlpSpec, LinearHeadSpec, ModelSpec, NoPositionSpec,
                    RmsNormSpec, RotarySpec, ScheduleEntry)
 from .registry import (Architecture, architecture, architecture_of, known_architectures,
@@ -57,7 +58,20 @@ register_architecture(Architecture(
     complete_config=_mekevik.with_sizes_of,
 ))
 
+from . import netanex as _netanex
+from .netanex import NetanexConfig
+
+register_architecture(Architecture(
+    name=_netanex.ARCHITECTURE,
+    read_config=NetanexConfig.from_dict,
+    to_spec=NetanexConfig.to_spec,
+    tensor_name=_netanex.tensor_name,
+    cap_positions=NetanexConfig.with_max_positions,
+    config_to_dict=NetanexConfig.to_dict,
+))
+
 __all__ = [
+    "NetanexConfig", "NormedAttentionSpec", "RotaryBlendSpec", "SandwichBlockSpec",
     "AttentionSpec", "BlockSpec", "ConfigError", "GatedMlpSpec", "LinearHeadSpec", "ModelSpec", "NoPositionSpec",
     "RmsNormSpec", "RotarySpec", "ScheduleEntry", "Architecture", "architecture", "architecture_of",
     "known_architectures", "read_config_json", "register_architecture", "unregister_architecture",

@@ -27,6 +27,7 @@ class RmsNormSpec:
     eps: float
     kind: str = "rmsnorm"
     optional: bool = False  # the file may lack the gain; the norm is then not applied by who owns it
+    one_plus: bool = False  # the stored gain sits around zero: the factor is 1 + w
 
 
 @dataclass(frozen=True)
@@ -53,6 +54,26 @@ class RotaryPairsSpec:
     base: float
     scaling: Optional[Tuple[float, float, float, float]] = None
     kind: str = "rotary_pairs"
+
+
+@dataclass(frozen=True)
+class RotaryBlendSpec:
+    """Rotary position encoding over a table of frequencies base^(-2i/dims) whose slow ones are divided by ``factor``:
+    with turns(t) = dims * ln(original / (2 pi t)) / (2 ln base), lo = max(floor(turns(fast)), 0),
+    hi = min(ceil(turns(slow)), dims - 1) and ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1) the frequency
+    is f_i / factor * ramp_i + f_i * (1 - ramp_i); cos and sin are both multiplied by
+    ``magnitude_slope`` * ln(factor) + 1.  ``factor`` 1: the plain table.  ``pairing`` "halves": number i is turned
+    with number i + dims / 2; "neighbours": number 2i with number 2i + 1."""
+
+    dims: int
+    base: float
+    factor: float = 1.0
+    original: float = 0.0
+    fast: float = 32.0
+    slow: float = 1.0
+    magnitude_slope: float = 0.1
+    pairing: str = "halves"
+    kind: str = "rotary_blend"
 
 
 @dataclass(frozen=True)
@@ -116,6 +137,37 @@ class BiasAttentionSpec:
 
 
 @dataclass(frozen=True)
+class NormedAttentionSpec:
+    """Causal softmax attention with grouped key/value heads whose queries and keys pass an RMS norm with a gain,
+    per head (``qk_norm`` "head": one gain of ``head_dim`` numbers for all heads) or over the whole projection of
+    a token (``qk_norm`` "whole": all heads at once, gains as wide as the projections); biases on the projections;
+    a factor 1 + ``temp_coef`` * ln(floor((position + 1) / ``temp_every``) + 1) on the queries; a sink in the
+    softmax's denominator (``sink`` "zero": a score of 0, "learned": a score per head); a logistic gate per head.
+    ``maps`` 2: every head has two maps of scores (queries and keys twice as wide, [map 1 | map 2]) over the same
+    values, combined as a1 - lambda a2 with lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + ``diff``, divided by its
+    root mean square over the head's values and multiplied by 1 - ``diff``."""
+
+    width: int
+    n_heads: int
+    n_kv_heads: int
+    head_dim: int
+    v_head_dim: int
+    scale: float
+    window: int = 0  # 0: every earlier key; w > 0: the last w keys
+    qk_norm: str = "none"  # "none" | "head" | "whole"
+    norm_eps: float = 1e-6
+    proj_bias: bool = False  # biases on the query, key and value projections
+    out_bias: bool = False  # a bias on the output projection
+    temp_coef: float = 0.0
+    temp_every: int = 0  # 0: no factor on the queries
+    sink: str = "none"  # "none" | "zero" | "learned"
+    head_gate: bool = False
+    maps: int = 1
+    diff: float = 0.0
+    kind: str = "normed_attention"
+
+
+@dataclass(frozen=True)
 class SigmoidAttentionSpec:
     """Causal attention without a softmax: a visible key weighs sigmoid(q . k * scale + bias) and nothing is
     normalised over the keys.  Grouped key/value heads with value heads of a width of their own; optionally an
@@ -147,10 +199,13 @@ class SigmoidAttentionSpec:
 
 @dataclass(frozen=True)
 class LatentAttentionSpec:
-    """Softmax attention through low-rank latents: queries from a normed latent of ``q_rank`` numbers; per token
+    """Softmax attention through low-rank latents: queries from a normed latent of ``q_rank`` numbers (0: straight
+    from the mixer's input); per token
     one normed latent of ``kv_rank`` numbers, from which every head's unrotated keys (``head_dim``) and values
     (``v_head_dim``) come, and one rotated key part of ``rot_dim`` numbers that all heads share.  Only the latent
-    and the rotated part are cached.  ``window``: the last so many keys (0: all); a logistic gate per head."""
+    and the rotated part are cached.  ``window``: the last so many keys (0: all); a logistic gate per head
+    (``head_gate``) or per output number (``element_gate``); ``sink``: a learned score per head in the softmax's
+    denominator, without a key or a value."""
 
     width: int
     n_heads: int
@@ -164,6 +219,8 @@ class LatentAttentionSpec:
     norm_eps: float
     window: int = 0
     head_gate: bool = True
+    element_gate: bool = False
+    sink: bool = False
     kind: str = "latent_attention"
 
 
@@ -213,7 +270,10 @@ class MoeSpec:
     slope: float = 1.702  # the activation is g * sigmoid(slope * g) * (u + 1)
     weight_on_input: bool = True  # the router weight multiplies the expert's input (False: its output)
     renormalise: bool = False  # divide the chosen experts' weights by their sum
-    scores: str = "sigmoid"  # the router's scores: "sigmoid" of each logit, or "softmax" over all experts
+    # the router's scores: "sigmoid" of each logit, or "softmax" over all experts; "table": no router, a table
+    # [``table_rows``, top] of expert ids by token id chooses, and every chosen expert weighs 1 / top
+    scores: str = "sigmoid"
+    table_rows: int = 0
     weight_scale: float = 1.0  # factor on the (renormalised) weights
     renormalise_eps: float = 0.0  # added to the sum the weights are divided by
     activation: str = "limited"  # "limited": the clamped unit above; "silu" / "gelu_tanh": act(g) * u, no clamps
@@ -265,6 +325,22 @@ class PostNormBlockSpec:
     ffn_norm: Any
     alpha: float = 1.0
     kind: str = "post_norm"
+
+
+@dataclass(frozen=True)
+class SandwichBlockSpec:
+    """A block with a norm before and after each sublayer: x <- x + post(mixer(pre(x))), then
+    x <- x + ffn_post(ffn(ffn_pre(x))).  ``ffn`` may be None (the second step is then left out).  ``label``: the
+    name under which the block's parameters are listed (``blocks.<label>...``) when it is not its index."""
+
+    mixer: Any
+    ffn: Any
+    mixer_norm: Any
+    mixer_post_norm: Any
+    ffn_norm: Any = None
+    ffn_post_norm: Any = None
+    label: Optional[str] = None
+    kind: str = "sandwich"
 
 
 @dataclass(frozen=True)
@@ -332,6 +408,7 @@ class ModelSpec:
     max_positions: int
     tie_embeddings: bool = False
     embedding_scale: float = 1.0
+    embedding_norm: Any = None  # a norm spec: the embedding rows are normed before the first block reads them
     stop_ids: Tuple[int, ...] = field(default_factory=tuple)
     head: Any = field(default_factory=LinearHeadSpec)  # a head spec; its part turns normed rows into logits
 

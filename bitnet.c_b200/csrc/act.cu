@@ -232,3 +232,31 @@ extern "C" int bn_gated_lookup(const void* pre, int pre_stride, int dtype, const
             table_stride, col0, vocab, tokens, out, dim, total, act);
   return BN_OK;
 }
+
+// x[t, i] <- x[t, i] * sigmoid(g[t, i]) for i < n, in place: an output gate on every number of a row.  x and g are
+// views into rows of `dtype` with strides of their own; the logistic function is taken in float32.
+template <typename T>
+__global__ void gate_rows_kernel(T* __restrict__ x, int x_stride, const T* __restrict__ g, int g_stride, int n, size_t total) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = i / n, c = i - t * n;
+    const float z = to_f32<T>(g[t * g_stride + c]);
+    x[t * x_stride + c] = from_f32<T>(to_f32<T>(x[t * x_stride + c]) / (1.0f + expf(-z)));
+  }
+}
+
+extern "C" int bn_gate_rows(void* x, int x_stride, const void* g, int g_stride, int dtype, int n_rows, int n, cudaStream_t stream) {
+  if (n_rows <= 0 || n <= 0) return BN_OK;
+  if (!x || !g || x_stride < n || g_stride < n) return BN_ERR_BAD_ARG;
+  const size_t total = (size_t)n_rows * n;
+  const unsigned blocks = (unsigned)min((size_t)4096, (total + 255) / 256);
+  if (dtype == BN_F32)
+    BN_LAUNCH(gate_rows_kernel<float>, blocks, 256, 0, stream, (float*)x, x_stride, (const float*)g, g_stride, n, total);
+  else if (dtype == BN_BF16)
+    BN_LAUNCH(gate_rows_kernel<__nv_bfloat16>, blocks, 256, 0, stream, (__nv_bfloat16*)x, x_stride, (const __nv_bfloat16*)g,
+              g_stride, n, total);
+  else
+    return BN_ERR_BAD_ARG;
+  return BN_OK;
+}

@@ -38,6 +38,20 @@ struct Vec16<__nv_bfloat16> {
   }
 };
 
+// 1 / (l + e^(sink - m)) for sums l taken relative to the maximum m, also when the sink exceeds every score
+__device__ __forceinline__ float sink_inverse(float m, float l, float sink) {
+  const float top = fmaxf(m, sink);
+  const float a = expf(m - top);
+  return a / (l * a + expf(sink - top));
+}
+
+// a result number: in the compute type, or (out_wide) as float32 into an output that is a float32 array
+template <typename T>
+__device__ __forceinline__ void store_result(T* out, int out_wide, size_t at, float v) {
+  if (out_wide) reinterpret_cast<float*>(out)[at] = v;
+  else out[at] = from_f32<T>(v);
+}
+
 // Optional extras, each off when its pointer is null or its number zero, so that one kernel
 // serves every softmax attention of the library:
 //   v_dim        width of a value head when it differs from a key head's
@@ -49,6 +63,11 @@ struct Vec16<__nv_bfloat16> {
 //                chunk only (takes the place of the window)
 //   v_row        width of a row of the value plane when it is more than v_dim: the values are the first
 //                v_dim numbers of each row (the key plane itself, for values that are a part of the keys)
+//   sink         per head a score (float32) that stands in the softmax's denominator once, without a key and
+//                without a value: the weights then sum to less than one
+//   out_wide     the output is a float32 array whatever the compute type (what follows wants the sums unrounded)
+//   v_share      so many consecutive key heads read one value head (the value plane has n_kv_heads / v_share
+//                heads): several maps of scores over the same values
 template <typename T>
 __global__ void attention_general_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out,
                                          int out_stride, int n_heads, int n_kv_heads, int head_dim, int v_dim,
@@ -58,7 +77,7 @@ __global__ void attention_general_kernel(const T* __restrict__ q, int q_stride, 
                                          const int* __restrict__ tok_pos, const int* __restrict__ slots,
                                          const int* __restrict__ page_table, int pt_stride,
                                          const T* __restrict__ k_cache, const T* __restrict__ v_cache,
-                                         float* __restrict__ part, int n_splits) {
+                                         float* __restrict__ part, int n_splits, const float* __restrict__ sink, int v_share, int out_wide) {
   pdl_launch_dependents();  // the next kernel in the stream may begin its prologue
   pdl_wait();               // the kernels before this one have completed and their writes are visible
   extern __shared__ __align__(16) float sm[];
@@ -67,6 +86,7 @@ __global__ void attention_general_kernel(const T* __restrict__ q, int q_stride, 
   float* scratch = ps + ATT_CHUNK;   // 32
   int t = blockIdx.x, h = blockIdx.y;
   int kvh = h / (n_heads / n_kv_heads);
+  const int vh = kvh / v_share, n_v_heads = n_kv_heads / v_share;
   int pos = tok_pos[t];
   const int* pt = page_table + (size_t)slots[tok_seq[t]] * pt_stride;
   int lo = chunk > 0 ? (pos / chunk) * chunk : (window > 0 ? max(0, pos - window + 1) : 0);
@@ -138,7 +158,7 @@ __global__ void attention_general_kernel(const T* __restrict__ q, int q_stride, 
           int u = base + j;
           int p = u < n_first ? u : lo + (u - n_first);
           float vv[VN];
-          Vec16<T>::load(v_cache + cache_row_offset(pt, p, n_kv_heads, kvh, v_row) + piece * VN, vv);
+          Vec16<T>::load(v_cache + cache_row_offset(pt, p, n_v_heads, vh, v_row) + piece * VN, vv);
           float w = ps[j];
 #pragma unroll
           for (int e = 0; e < VN; ++e) accv[e] = fmaf(w, vv[e], accv[e]);
@@ -153,7 +173,7 @@ __global__ void attention_general_kernel(const T* __restrict__ q, int q_stride, 
           for (int j = 0; j < n; ++j) {
             int u = base + j;
             int p = u < n_first ? u : lo + (u - n_first);
-            const T* vrow = v_cache + cache_row_offset(pt, p, n_kv_heads, kvh, v_row);
+            const T* vrow = v_cache + cache_row_offset(pt, p, n_v_heads, vh, v_row);
             a = fmaf(ps[j], to_f32<T>(vrow[d]), a);
           }
           acc[r] = a;
@@ -162,9 +182,9 @@ __global__ void attention_general_kernel(const T* __restrict__ q, int q_stride, 
     }
     __syncthreads();  // ps[] is rewritten by the next chunk
   }
-  float inv = 1.0f / l_run;
+  float inv = sink && !part ? sink_inverse(m_run, l_run, sink[h]) : 1.0f / l_run;
   if (gate) inv *= 1.0f / (1.0f + expf(-to_f32<T>(gate[(size_t)t * gate_stride + h])));
-  T* orow = out + (size_t)t * out_stride + (size_t)h * v_dim;
+  const size_t orow = (size_t)t * out_stride + (size_t)h * v_dim;
   float* prow = part ? part + (((size_t)t * n_heads + h) * n_splits + blockIdx.z) * (v_dim + 2) : nullptr;
   if (prow && threadIdx.x == 0) { prow[0] = m_run; prow[1] = l_run; }
   if (wide) {
@@ -179,7 +199,7 @@ __global__ void attention_general_kernel(const T* __restrict__ q, int q_stride, 
       float a = 0.f;
       for (int g = 0; g < groups; ++g) a += red[(size_t)g * v_dim + d];
       if (prow) prow[2 + d] = a;
-      else orow[d] = from_f32<T>(a * inv);
+      else store_result<T>(out, out_wide, orow + d, a * inv);
     }
     return;
   }
@@ -188,7 +208,7 @@ __global__ void attention_general_kernel(const T* __restrict__ q, int q_stride, 
     int d = threadIdx.x + r * ATT_THREADS;
     if (d < v_dim) {
       if (prow) prow[2 + d] = acc[r];
-      else orow[d] = from_f32<T>(acc[r] * inv);
+      else store_result<T>(out, out_wide, orow + d, acc[r] * inv);
     }
   }
 }
@@ -224,7 +244,8 @@ attention_grouped_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
                          int v_row, const float* __restrict__ rel, int n_rel, const T* __restrict__ gate, int gate_stride,
                          const int* __restrict__ tok_seq, const int* __restrict__ tok_pos, const int* __restrict__ slots,
                          const int* __restrict__ page_table, int pt_stride, const T* __restrict__ k_cache,
-                         const T* __restrict__ v_cache, float* __restrict__ part, int n_splits) {
+                         const T* __restrict__ v_cache, float* __restrict__ part, int n_splits,
+                         const float* __restrict__ sink, int v_share, int out_wide) {
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ __align__(16) float sm[];
@@ -234,6 +255,7 @@ attention_grouped_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
   float* red = scratch + 32 * R;            // [R][groups * v_dim] at the end
   const int t = blockIdx.x, h0 = blockIdx.y * R;
   const int kvh = h0 / (n_heads / n_kv_heads);
+  const int vh = kvh / v_share, n_v_heads = n_kv_heads / v_share;
   const int pos = tok_pos[t];
   const int* pt = page_table + (size_t)slots[tok_seq[t]] * pt_stride;
   const int lo = chunk > 0 ? (pos / chunk) * chunk : (window > 0 ? max(0, pos - window + 1) : 0);
@@ -317,7 +339,7 @@ attention_grouped_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
           if (j < n) {
             const int u = base + j;
             const int p = u < n_first ? u : lo + (u - n_first);
-            Vec16<T>::load(v_cache + cache_row_offset(pt, p, n_kv_heads, kvh, v_row) + piece * VN, vv[b]);
+            Vec16<T>::load(v_cache + cache_row_offset(pt, p, n_v_heads, vh, v_row) + piece * VN, vv[b]);
           }
         }
 #pragma unroll
@@ -347,16 +369,16 @@ attention_grouped_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
 #pragma unroll
   for (int r = 0; r < R; ++r) {
     const int h = h0 + r;
-    float inv = 1.0f / l_run[r];
+    float inv = sink && !part ? sink_inverse(m_run[r], l_run[r], sink[h]) : 1.0f / l_run[r];
     if (gate) inv *= 1.0f / (1.0f + expf(-to_f32<T>(gate[(size_t)t * gate_stride + h])));
-    T* orow = out + (size_t)t * out_stride + (size_t)h * v_dim;
+    const size_t orow = (size_t)t * out_stride + (size_t)h * v_dim;
     float* prow = part ? part + (((size_t)t * n_heads + h) * n_splits + blockIdx.z) * (v_dim + 2) : nullptr;
     if (prow && threadIdx.x == 0) { prow[0] = m_run[r]; prow[1] = l_run[r]; }
     for (int d = threadIdx.x; d < v_dim; d += ATT_THREADS) {
       float a = 0.f;
       for (int g = 0; g < groups; ++g) a += red[((size_t)r * groups + g) * v_dim + d];
       if (prow) prow[2 + d] = a;
-      else orow[d] = from_f32<T>(a * inv);
+      else store_result<T>(out, out_wide, orow + d, a * inv);
     }
   }
 }
@@ -364,7 +386,8 @@ attention_grouped_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
 // out[t][h] = sum_z e^{m_z - M} acc_z / sum_z e^{m_z - M} l_z (times the logistic function of the gate), M = max_z m_z
 template <typename T>
 __global__ void attention_merge_kernel(const float* __restrict__ part, int n_splits, int n_heads, int v_dim,
-                                       const T* __restrict__ gate, int gate_stride, T* __restrict__ out, int out_stride) {
+                                       const T* __restrict__ gate, int gate_stride, T* __restrict__ out, int out_stride,
+                                       const float* __restrict__ sink, int out_wide) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x, h = blockIdx.y;
@@ -376,7 +399,7 @@ __global__ void attention_merge_kernel(const float* __restrict__ part, int n_spl
     float m = p[(size_t)z * (v_dim + 2)];
     if (m != -INFINITY) L += expf(m - M) * p[(size_t)z * (v_dim + 2) + 1];
   }
-  float inv = 1.0f / L;
+  float inv = sink ? sink_inverse(M, L, sink[h]) : 1.0f / L;
   if (gate) inv *= 1.0f / (1.0f + expf(-to_f32<T>(gate[(size_t)t * gate_stride + h])));
   for (int d = threadIdx.x; d < v_dim; d += blockDim.x) {
     float a = 0.f;
@@ -384,7 +407,7 @@ __global__ void attention_merge_kernel(const float* __restrict__ part, int n_spl
       float m = p[(size_t)z * (v_dim + 2)];
       if (m != -INFINITY) a = fmaf(expf(m - M), p[(size_t)z * (v_dim + 2) + 2 + d], a);
     }
-    out[(size_t)t * out_stride + (size_t)h * v_dim + d] = from_f32<T>(a * inv);
+    store_result<T>(out, out_wide, (size_t)t * out_stride + (size_t)h * v_dim + d, a * inv);
   }
 }
 
@@ -396,8 +419,9 @@ extern "C" int bn_attention_general_ex(const void* q, int q_stride, void* out, i
                                        const void* gate, int gate_stride, const int* tok_seq, const int* tok_pos, const int* slots,
                                        const int* page_table, int pt_stride,
                                        const void* k_cache, const void* v_cache, float* part, int n_splits,
-                                       cudaStream_t stream) {
+                                       const float* sink, int v_share, int out_wide, cudaStream_t stream) {
   if (n_tokens <= 0) return BN_OK;
+  if (v_share < 1 || n_kv_heads % v_share || (v_share > 1 && v_row > 0)) return BN_ERR_BAD_ARG;
   if (n_splits < 1 || n_splits > 64 || (n_splits > 1 && !part)) return BN_ERR_BAD_ARG;
   if (n_splits == 1) part = nullptr;
   if (v_row <= 0) v_row = v_dim;
@@ -428,7 +452,7 @@ extern "C" int bn_attention_general_ex(const void* q, int q_stride, void* out, i
     BN_LAUNCH((attention_grouped_kernel<TT, RR>), ggrid, ATT_THREADS, gsmem, stream, (const TT*)q, q_stride, (TT*)out,       \
               out_stride, n_heads, n_kv_heads, head_dim, v_dim, scale, window, keep_first, chunk, v_row, rel, n_rel,        \
               (const TT*)gate, gate_stride, tok_seq, tok_pos, slots, page_table, pt_stride, (const TT*)k_cache,              \
-              (const TT*)v_cache, part, n_splits);                                                                          \
+              (const TT*)v_cache, part, n_splits, sink, v_share, out_wide);                                                           \
   } while (0)
     if (gsmem <= 160 * 1024 && (dtype == BN_F32 || dtype == BN_BF16)) {
       if (dtype == BN_F32) { if (R == 4) BN_GROUPED(float, 4); else BN_GROUPED(float, 2); }
@@ -438,10 +462,10 @@ extern "C" int bn_attention_general_ex(const void* q, int q_stride, void* out, i
         dim3 mgrid(n_tokens, n_heads);
         if (dtype == BN_F32)
           BN_LAUNCH((attention_merge_kernel<float>), mgrid, 128, 0, stream, (const float*)part, n_splits, n_heads, v_dim,
-                    (const float*)gate, gate_stride, (float*)out, out_stride);
+                    (const float*)gate, gate_stride, (float*)out, out_stride, sink, out_wide);
         else
           BN_LAUNCH((attention_merge_kernel<__nv_bfloat16>), mgrid, 128, 0, stream, (const float*)part, n_splits, n_heads, v_dim,
-                    (const __nv_bfloat16*)gate, gate_stride, (__nv_bfloat16*)out, out_stride);
+                    (const __nv_bfloat16*)gate, gate_stride, (__nv_bfloat16*)out, out_stride, sink, out_wide);
       }
       BN_CHECK_LAUNCH();
       return BN_OK;
@@ -453,23 +477,23 @@ extern "C" int bn_attention_general_ex(const void* q, int q_stride, void* out, i
     BN_LAUNCH((attention_general_kernel<float>), grid, ATT_THREADS, smem, stream, 
         (const float*)q, q_stride, (float*)out, out_stride, n_heads, n_kv_heads, head_dim, v_dim, scale, window,
         keep_first, chunk, v_row, rel, n_rel, (const float*)gate, gate_stride,
-        tok_seq, tok_pos, slots, page_table, pt_stride, (const float*)k_cache, (const float*)v_cache, part, n_splits);
+        tok_seq, tok_pos, slots, page_table, pt_stride, (const float*)k_cache, (const float*)v_cache, part, n_splits, sink, v_share, out_wide);
   else if (dtype == BN_BF16)
     BN_LAUNCH((attention_general_kernel<__nv_bfloat16>), grid, ATT_THREADS, smem, stream, 
         (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, n_heads, n_kv_heads, head_dim, v_dim,
         scale, window, keep_first, chunk, v_row, rel, n_rel, (const __nv_bfloat16*)gate, gate_stride,
         tok_seq, tok_pos, slots, page_table, pt_stride,
-        (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, part, n_splits);
+        (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, part, n_splits, sink, v_share, out_wide);
   else
     return BN_ERR_BAD_ARG;
   if (part) {
     dim3 mgrid(n_tokens, n_heads);
     if (dtype == BN_F32)
       BN_LAUNCH((attention_merge_kernel<float>), mgrid, 128, 0, stream, (const float*)part, n_splits, n_heads, v_dim,
-                (const float*)gate, gate_stride, (float*)out, out_stride);
+                (const float*)gate, gate_stride, (float*)out, out_stride, sink, out_wide);
     else
       BN_LAUNCH((attention_merge_kernel<__nv_bfloat16>), mgrid, 128, 0, stream, (const float*)part, n_splits, n_heads, v_dim,
-                (const __nv_bfloat16*)gate, gate_stride, (__nv_bfloat16*)out, out_stride);
+                (const __nv_bfloat16*)gate, gate_stride, (__nv_bfloat16*)out, out_stride, sink, out_wide);
   }
   BN_CHECK_LAUNCH();
   return BN_OK;
@@ -482,5 +506,5 @@ extern "C" int bn_attention_general(const void* q, int q_stride, void* out, int 
                                     const void* k_cache, const void* v_cache, cudaStream_t stream) {
   return bn_attention_general_ex(q, q_stride, out, out_stride, dtype, n_tokens, n_heads, n_kv_heads, head_dim, head_dim,
                                  scale, window, 0, 0, 0, nullptr, 0, nullptr, 0, tok_seq, tok_pos, slots, page_table,
-                                 pt_stride, k_cache, v_cache, nullptr, 1, stream);
+                                 pt_stride, k_cache, v_cache, nullptr, 1, nullptr, 1, 0, stream);
 }

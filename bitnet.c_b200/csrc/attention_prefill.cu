@@ -42,7 +42,8 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
                          const int* __restrict__ tile_seq, const int* __restrict__ tile_row0,
                          const int* __restrict__ seq_start, const int* __restrict__ seq_pos0,
                          const int* __restrict__ slots, const int* __restrict__ page_table, int pt_stride,
-                         const __nv_bfloat16* __restrict__ k_cache, const __nv_bfloat16* __restrict__ v_cache) {
+                         const __nv_bfloat16* __restrict__ k_cache, const __nv_bfloat16* __restrict__ v_cache,
+                         const float* __restrict__ sink, int v_share, int out_wide) {
   pdl_launch_dependents();  // the next kernel in the stream may begin its prologue
   pdl_wait();               // the kernels before this one have completed and their writes are visible
   extern __shared__ __align__(128) unsigned char smem[];
@@ -91,7 +92,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
   auto load_kv = [&](int tile, int stage) {
     int page = pt[tile];
     const __nv_bfloat16* kb = k_cache + ((size_t)page * n_kv_heads + kvh) * BN_PAGE * head_dim;
-    const __nv_bfloat16* vb = v_cache + ((size_t)page * n_kv_heads + kvh) * BN_PAGE * v_row;  // v_row >= v_dim: the row's first v_dim numbers
+    const __nv_bfloat16* vb = v_cache + ((size_t)page * (n_kv_heads / v_share) + kvh / v_share) * BN_PAGE * v_row;  // v_row >= v_dim: the row's first v_dim numbers
     for (int p = tid; p < PF_N * CHUNKS; p += PF_THREADS) {
       int r = p / CHUNKS, c = p % CHUNKS;
       bool ok = c < real_chunks;
@@ -249,14 +250,23 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
     int r = warp * 16 + g + e * 8;
     if (r >= rows_here) continue;
     float inv = 1.0f / l_run[e];
+    if (sink) {
+      // a score in the denominator that has no key and no value (the running maximum is in units of log2)
+      const float s2 = sink[h] * 1.4426950408889634f, top = fmaxf(m_run[e], s2), a = exp2f(m_run[e] - top);
+      inv = a / (l_run[e] * a + exp2f(s2 - top));
+    }
     if (gate) inv *= 1.0f / (1.0f + expf(-__bfloat162float(gate[(size_t)(start + row0 + r) * gate_stride + h])));
-    __nv_bfloat16* orow = out + (size_t)(start + row0 + r) * out_stride + (size_t)h * v_dim;
+    const size_t oat = (size_t)(start + row0 + r) * out_stride + (size_t)h * v_dim;
 #pragma unroll
     for (int j = 0; j < NT_O; ++j) {
       int d = j * 8 + 2 * t;
       if (d < v_dim) {
-        __nv_bfloat162 v = __floats2bfloat162_rn(o[j][2 * e] * inv, o[j][2 * e + 1] * inv);
-        *reinterpret_cast<__nv_bfloat162*>(orow + d) = v;
+        if (out_wide) {  // the output is a float32 array: the sums unrounded
+          *reinterpret_cast<float2*>(reinterpret_cast<float*>(out) + oat + d) = make_float2(o[j][2 * e] * inv, o[j][2 * e + 1] * inv);
+        } else {
+          __nv_bfloat162 v = __floats2bfloat162_rn(o[j][2 * e] * inv, o[j][2 * e + 1] * inv);
+          *reinterpret_cast<__nv_bfloat162*>(out + oat + d) = v;
+        }
       }
     }
   }
@@ -268,7 +278,7 @@ static int launch_prefill(const void* q, int q_stride, void* out, int out_stride
                           const float* rel, int n_rel, const void* gate, int gate_stride, const int* tile_seq,
                           const int* tile_row0, const int* seq_start, const int* seq_pos0, const int* slots,
                           const int* page_table, int pt_stride, const void* k_cache, const void* v_cache,
-                          cudaStream_t stream) {
+                          const float* sink, int v_share, int out_wide, cudaStream_t stream) {
   size_t smem = (size_t)PF_M * HD * 2 + 2 * (size_t)PF_N * HD * 2 + 2 * (size_t)PF_N * VD * 2;
   static bool configured = false;
   if (!configured) {
@@ -282,7 +292,7 @@ static int launch_prefill(const void* q, int q_stride, void* out, int out_stride
   BN_LAUNCH((attention_prefill_kernel<HD, PRECISE, VD>), grid, PF_THREADS, smem, stream, 
       (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, n_heads, n_kv_heads, head_dim, v_dim,
       scale * 1.4426950408889634f, window, keep_first, chunk, v_row, rel, n_rel, (const __nv_bfloat16*)gate, gate_stride, tile_seq, tile_row0, seq_start, seq_pos0, slots, page_table, pt_stride,
-      (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache);
+      (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, sink, v_share, out_wide);
   BN_CHECK_LAUNCH();
   return BN_OK;
 }
@@ -295,14 +305,19 @@ static int launch_prefill(const void* q, int q_stride, void* out, int out_stride
 // one); gate [tokens, gate_stride] holds per token and head a number whose logistic function
 // multiplies the head's output; chunk: positions are cut into chunks of so many and a query sees the
 // earlier keys of its own chunk (in place of a window); v_row: the width of a row of the value
-// plane when the values are the first v_dim numbers of wider rows (0: v_dim).
+// plane when the values are the first v_dim numbers of wider rows (0: v_dim); sink [n_heads] float32: a score
+// per head that stands in the softmax's denominator once, with no key and no value; v_share: so many
+// consecutive key heads read one value head (the value plane has n_kv_heads / v_share heads); out_wide: out is
+// a float32 array.
 extern "C" int bn_attention_prefill_ex(const void* q, int q_stride, void* out, int out_stride, int n_tiles, int n_heads,
                                        int n_kv_heads, int head_dim, int v_dim, float scale, int window, int keep_first,
                                        int chunk, int v_row, const float* rel, int n_rel, const void* gate, int gate_stride, int precise,
                                        const int* tile_seq, const int* tile_row0, const int* seq_start,
                                        const int* seq_pos0, const int* slots, const int* page_table, int pt_stride,
-                                       const void* k_cache, const void* v_cache, cudaStream_t stream) {
+                                       const void* k_cache, const void* v_cache, const float* sink, int v_share, int out_wide,
+                                       cudaStream_t stream) {
   if (n_tiles <= 0) return BN_OK;
+  if (v_share < 1 || n_kv_heads % v_share || (v_share > 1 && v_row > 0)) return BN_ERR_BAD_ARG;
   if (v_row <= 0) v_row = v_dim;
   if (chunk < 0 || (chunk > 0 && (window > 0 || keep_first > 0)) || v_row < v_dim || v_row % 8) return BN_ERR_BAD_ARG;
   if (head_dim <= 0 || head_dim % 16 || head_dim > 256 || n_kv_heads <= 0 || n_heads % n_kv_heads || window < 0 ||
@@ -311,7 +326,7 @@ extern "C" int bn_attention_prefill_ex(const void* q, int q_stride, void* out, i
     return BN_ERR_BAD_ARG;
 #define BN_PF_ARGS q, q_stride, out, out_stride, n_tiles, n_heads, n_kv_heads, head_dim, v_dim, scale, window, keep_first, chunk, v_row, rel, \
                    n_rel, gate, gate_stride, tile_seq, tile_row0, seq_start, seq_pos0, slots, page_table, pt_stride,      \
-                   k_cache, v_cache, stream
+                   k_cache, v_cache, sink, v_share, out_wide, stream
   if (precise) {
     // key and value heads of their own widths: the instantiation for each
     const int hd = head_dim <= 64 ? 64 : head_dim <= 128 ? 128 : 256, vd = v_dim <= 64 ? 64 : v_dim <= 128 ? 128 : 256;
@@ -338,5 +353,5 @@ extern "C" int bn_attention_prefill(const void* q, int q_stride, void* out, int 
                                     const void* v_cache, cudaStream_t stream) {
   return bn_attention_prefill_ex(q, q_stride, out, out_stride, n_tiles, n_heads, n_kv_heads, head_dim, head_dim, scale, window, 0,
                                  0, 0, nullptr, 0, nullptr, 0, 0, tile_seq, tile_row0, seq_start, seq_pos0, slots, page_table,
-                                 pt_stride, k_cache, v_cache, stream);
+                                 pt_stride, k_cache, v_cache, nullptr, 1, 0, stream);
 }

@@ -379,3 +379,31 @@ extern "C" int bn_moe_gather(const void* y_sorted, int dtype, int n_tokens, int 
   BN_CHECK_LAUNCH();
   return BN_OK;
 }
+
+// Experts by a table instead of a router: token id -> the `top` experts of its row, each with the same weight.
+// table [vocab, table_stride] int32; an id outside the table, or an entry outside the experts, takes expert 0
+// with weight 0 (it adds nothing).
+__global__ void moe_table_route_kernel(const int* __restrict__ tokens, int n_tokens, const int* __restrict__ table, int vocab,
+                                       int table_stride, int top, int n_experts, float weight, int* __restrict__ ids,
+                                       float* __restrict__ weights) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_tokens * top) return;
+  const int t = i / top, k = i - t * top;
+  const int tok = tokens[t];
+  int e = tok >= 0 && tok < vocab ? table[(size_t)tok * table_stride + k] : -1;
+  const bool ok = e >= 0 && e < n_experts;
+  ids[i] = ok ? e : 0;
+  weights[i] = ok ? weight : 0.f;
+}
+
+extern "C" int bn_moe_table_route(const int* tokens, int n_tokens, const int* table, int vocab, int table_stride, int top,
+                                  int n_experts, float weight, int* ids, float* weights, cudaStream_t stream) {
+  if (n_tokens <= 0) return BN_OK;
+  if (!tokens || !table || !ids || !weights || top <= 0 || top > table_stride || vocab <= 0 || n_experts <= 0) return BN_ERR_BAD_ARG;
+  BN_LAUNCH(moe_table_route_kernel, (n_tokens * top + 255) / 256, 256, 0, stream, tokens, n_tokens, table, vocab, table_stride, top,
+            n_experts, weight, ids, weights);
+  BN_CHECK_LAUNCH();
+  return BN_OK;
+}

@@ -367,6 +367,85 @@ def slice_norm_append(x: torch.Tensor, q_len: int, wq: torch.Tensor, k_off: int,
         _ptr(page_table), int(pt_stride), _ptr(k_cache), _ptr(v_cache), _stream()), "slice_norm_append")
 
 
+def qk_norm_append(src: torch.Tensor, out: torch.Tensor, tok_pos: torch.Tensor, *, q_len: int, k_off: int, k_len: int,
+                   bias: Optional[torch.Tensor] = None, q_span: int = 0, wq: Optional[torch.Tensor] = None, k_span: int = 0,
+                   wk: Optional[torch.Tensor] = None, eps: float = 1e-6, temp_coef: float = 0.0, temp_every: int = 0,
+                   v_off: int = 0, n_kv_heads: int = 0, head_dim: int = 0, n_v_heads: int = 0, v_dim: int = 0,
+                   tok_seq: Optional[torch.Tensor] = None, slots: Optional[torch.Tensor] = None,
+                   page_table: Optional[torch.Tensor] = None, k_cache: Optional[torch.Tensor] = None,
+                   v_cache: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Queries, keys and values from the float32 rows ``src`` of their stacked projection into ``out`` (the same
+    columns, in the compute type): ``bias`` added; RMS norms with gains over spans of ``q_span`` numbers of the
+    first ``q_len`` (the queries) and of ``k_span`` numbers of the ``k_len`` at ``k_off`` (the keys) (a span of
+    one head norms heads one by one with one gain for all, a span of the whole slice norms all heads at once,
+    0: none); the queries times 1 + ``temp_coef`` * ln(floor((position + 1) / ``temp_every``) + 1) (0: no
+    factor); with a cache the keys (``n_kv_heads`` heads of ``head_dim``) and the values at ``v_off``
+    (``n_v_heads`` heads of ``v_dim``) are written into it."""
+    _need(src, "src", torch.float32, 2)
+    _need(out, "out", dims=2)
+    _need(tok_pos, "tok_pos", torch.int32, 1)
+    n, row = tok_pos.shape[0], src.shape[1]
+    if src.shape[0] < n or out.shape[0] < n or out.shape[1] != row or q_len > k_off or k_off + k_len > row:
+        raise KernelError("qk_norm_append: rows or slices do not fit")
+    if bias is not None:
+        _need(bias, "bias", dims=1)
+        if bias.shape[0] != row:
+            raise KernelError("qk_norm_append: the bias does not fit the row")
+    w_code = 0
+    for span, w, length, nm in ((q_span, wq, q_len, "wq"), (k_span, wk, k_len, "wk")):
+        if span:
+            _need(w, nm, dims=1)
+            if w.shape[0] != span or length % span:
+                raise KernelError(f"qk_norm_append: gain {nm} of {w.shape[0]} numbers does not fit spans of {span} in {length}")
+            if w_code and _code(w) != w_code:
+                raise KernelError("qk_norm_append: both gains must be of one type")
+            w_code = _code(w)
+    pt_stride = 0
+    if k_cache is not None:
+        for t, nm in ((tok_seq, "tok_seq"), (slots, "slots")):
+            _need(t, nm, torch.int32, 1)
+        _need(page_table, "page_table", torch.int32, 2)
+        _need(k_cache, "k_cache", out.dtype, 4)
+        _need(v_cache, "v_cache", out.dtype, 4)
+        if (tuple(k_cache.shape[1:]) != (n_kv_heads, PAGE, head_dim) or tuple(v_cache.shape) != (k_cache.shape[0], n_v_heads, PAGE, v_dim)
+                or k_len != n_kv_heads * head_dim or v_off < k_off + k_len or v_off + n_v_heads * v_dim > row):
+            raise KernelError(f"qk_norm_append: cache {tuple(k_cache.shape)} / {tuple(v_cache.shape)} does not fit")
+        pt_stride = page_table.shape[1]
+    _check(_fn("unit_norm", "bn_qk_norm_append")(
+        _ptr(src), int(src.stride(0)), _ptr(bias), int(_code(bias)) if bias is not None else 0, _ptr(out), int(_code(out)),
+        int(out.stride(0)), int(n), int(row), int(q_len), int(q_span), _ptr(wq) if q_span else _NULL, int(k_off), int(k_len),
+        int(k_span), _ptr(wk) if k_span else _NULL, int(w_code), c_float(eps), c_float(temp_coef), int(temp_every), int(v_off),
+        int(n_kv_heads), int(head_dim), int(n_v_heads), int(v_dim), _ptr(tok_seq), _ptr(tok_pos), _ptr(slots), _ptr(page_table),
+        int(pt_stride), _ptr(k_cache), _ptr(v_cache), _stream()), "qk_norm_append")
+    return out
+
+
+def diff_combine(maps: torch.Tensor, out: torch.Tensor, n_heads: int, per_group: int, v_dim: int, lam: float, eps: float,
+                 post: float) -> torch.Tensor:
+    """Two attention maps over the same values combined per token and head: o = a1 - ``lam`` a2, divided by its root
+    mean square over the head's ``v_dim`` numbers (``eps`` inside the root), times ``post``.  ``maps`` is float32
+    ``[n, 2 * n_heads * v_dim]`` with the maps of the ``per_group`` heads that share a key/value head laid out as
+    [group][map][head in group][v_dim]; ``out`` ``[n, n_heads * v_dim]`` holds the heads in their own order."""
+    _need(maps, "maps", torch.float32, 2)
+    _need(out, "out", dims=2)
+    if maps.shape[1] != 2 * n_heads * v_dim or out.shape[1] != n_heads * v_dim or out.shape[0] < maps.shape[0] or n_heads % per_group:
+        raise KernelError("diff_combine: sizes do not fit")
+    _check(_fn("unit_norm", "bn_diff_combine")(_ptr(maps), int(maps.stride(0)), _ptr(out), int(_code(out)), int(out.stride(0)),
+                                               int(maps.shape[0]), int(n_heads), int(per_group), int(v_dim), c_float(lam),
+                                               c_float(eps), c_float(post), _stream()), "diff_combine")
+    return out
+
+
+def gate_rows(x: torch.Tensor, g: torch.Tensor) -> torch.Tensor:
+    """x <- x * sigmoid(g), number by number, in place; x and g ``[n, m]`` views of one type with unit inner stride."""
+    if (not x.is_cuda or not g.is_cuda or x.dim() != 2 or g.dim() != 2 or x.dtype != g.dtype or x.stride(1) != 1
+            or g.stride(1) != 1 or g.shape[0] < x.shape[0] or g.shape[1] != x.shape[1]):
+        raise KernelError("gate_rows: x and g must be CUDA matrices of one type and width with unit inner stride")
+    _check(_fn("act", "bn_gate_rows")(c_void_p(x.data_ptr()), int(x.stride(0)), c_void_p(g.data_ptr()), int(g.stride(0)),
+                                      int(_code(x)), int(x.shape[0]), int(x.shape[1]), _stream()), "gate_rows")
+    return x
+
+
 # ---- attention ----------------------------------------------------------------------------
 def sigmoid_attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, n_tokens: int, n_heads: int, n_kv_heads: int,
                       head_dim: int, scale: float, window: int, tok_seq: torch.Tensor, tok_pos: torch.Tensor,
@@ -439,7 +518,8 @@ def attention_general(q: torch.Tensor, q_stride: int, out: torch.Tensor, n_token
                       tok_pos: torch.Tensor, slots: torch.Tensor, page_table: torch.Tensor,
                       k_cache: torch.Tensor, v_cache: torch.Tensor, *, keep_first: int = 0,
                       rel: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None,
-                      gate_stride: int = 0, max_keys: int = 0, chunk: int = 0, v_dim: int = 0) -> torch.Tensor:
+                      gate_stride: int = 0, max_keys: int = 0, chunk: int = 0, v_dim: int = 0,
+                      sink: Optional[torch.Tensor] = None, v_share: int = 1) -> torch.Tensor:
     """Causal attention of every new token over its sequence's pages; q may be a view into a wider row.
     ``max_keys`` (optional): a bound on the keys any of the tokens sees; with few tokens and many keys the
     keys of a token are then shared out over several blocks whose results a second kernel merges.
@@ -450,9 +530,18 @@ def attention_general(q: torch.Tensor, q_stride: int, out: torch.Tensor, n_token
     ``gate`` (a view with unit inner stride, row stride ``gate_stride``) holds one number per token and
     head whose logistic function multiplies the head's output.  ``chunk`` > 0 (in place of a window):
     positions are cut into chunks of so many and a token sees the earlier keys of its own chunk.
-    ``v_cache`` None with ``v_dim``: the values are the first ``v_dim`` numbers of the key rows."""
+    ``v_cache`` None with ``v_dim``: the values are the first ``v_dim`` numbers of the key rows.
+    ``sink`` float32 ``[n_heads]``: a score per head that stands in the softmax's denominator once, with no key
+    and no value.  ``v_share`` > 1: so many consecutive key heads read one value head (``v_cache`` has
+    ``n_kv_heads / v_share`` heads): several maps of scores over the same values."""
     if not q.is_cuda or q.stride(-1) != 1:
         raise KernelError("attention: q must be a CUDA tensor with unit inner stride")
+    if v_share < 1 or n_kv_heads % v_share or (v_share > 1 and v_cache is None):
+        raise KernelError(f"attention: {n_kv_heads} key heads cannot share values {v_share} at a time")
+    if sink is not None:
+        _need(sink, "sink", torch.float32, 1)
+        if sink.shape[0] != n_heads:
+            raise KernelError(f"attention: {sink.shape[0]} sink scores for {n_heads} heads")
     v_row = 0
     if v_cache is None:
         if not 0 < v_dim <= head_dim:
@@ -460,14 +549,18 @@ def attention_general(q: torch.Tensor, q_stride: int, out: torch.Tensor, n_token
         v_cache, v_row, inner = k_cache, head_dim, v_dim
     else:
         inner = v_cache.shape[3]
-    _need(out, "out", q.dtype, 2)
+    _need(out, "out", dims=2)
+    out_wide = out.dtype == torch.float32 and q.dtype != torch.float32  # the sums unrounded, whatever the compute type
+    if out.dtype != q.dtype and not out_wide:
+        raise KernelError(f"attention: out must be of q's type or float32, not {out.dtype}")
     for t, nm in ((tok_seq, "tok_seq"), (tok_pos, "tok_pos"), (slots, "slots")):
         _need(t, nm, torch.int32, 1)
     _need(page_table, "page_table", torch.int32, 2)
     _need(k_cache, "k_cache", q.dtype, 4)
     _need(v_cache, "v_cache", q.dtype, 4)
     v_dim = inner
-    if tuple(k_cache.shape[1:]) != (n_kv_heads, PAGE, head_dim) or tuple(k_cache.shape[:3]) != tuple(v_cache.shape[:3]):
+    if (tuple(k_cache.shape[1:]) != (n_kv_heads, PAGE, head_dim)
+            or tuple(v_cache.shape[:3]) != (k_cache.shape[0], n_kv_heads // v_share, PAGE)):
         raise KernelError(f"attention: cache {tuple(k_cache.shape)} / {tuple(v_cache.shape)} is not "
                           f"[pages, {n_kv_heads}, {PAGE}, {head_dim} / value width]")
     if not 0 < head_dim <= 2048 or v_dim > 1024:
@@ -498,7 +591,8 @@ def attention_general(q: torch.Tensor, q_stride: int, out: torch.Tensor, n_token
     blocks = n_tokens * n_heads // per_block
     if max_keys > 2 * DECODE_CHUNK and blocks < 2 * n_sms(q.device):
         splits = min(16, (max_keys + DECODE_CHUNK - 1) // DECODE_CHUNK, max(1, 4 * n_sms(q.device) // blocks))
-    if (keep_first or rel is not None or gate is not None or v_dim != head_dim or splits > 1 or chunk or v_row):
+    if (keep_first or rel is not None or gate is not None or v_dim != head_dim or splits > 1 or chunk or v_row
+            or sink is not None or v_share > 1 or out_wide):
         part = None
         if splits > 1:
             part = torch.empty(n_tokens * n_heads * splits * (v_dim + 2), dtype=torch.float32, device=q.device)
@@ -508,7 +602,8 @@ def attention_general(q: torch.Tensor, q_stride: int, out: torch.Tensor, n_token
             _ptr(q), int(q_stride), _ptr(out), int(out.shape[1]), int(_code(q)), int(n_tokens), int(n_heads),
             int(n_kv_heads), int(head_dim), int(v_dim), c_float(scale), int(window), int(keep_first), int(chunk), int(v_row),
             _ptr(rel), int(n_rel), _ptr(gate), int(gate_stride), _ptr(tok_seq), _ptr(tok_pos), _ptr(slots), _ptr(page_table),
-            int(page_table.shape[1]), _ptr(k_cache), _ptr(v_cache), _ptr(part), int(splits), _stream()), "attention_general")
+            int(page_table.shape[1]), _ptr(k_cache), _ptr(v_cache), _ptr(part), int(splits), _ptr(sink), int(v_share),
+            int(out_wide), _stream()), "attention_general")
         return out
     _check(_fn("attention", "bn_attention_general")(
         _ptr(q), int(q_stride), _ptr(out), int(out.shape[1]), int(_code(q)), int(n_tokens), int(n_heads),
@@ -523,12 +618,13 @@ def attention_prefill(q: torch.Tensor, q_stride: int, out: torch.Tensor, n_heads
                       seq_start: torch.Tensor, seq_pos0: torch.Tensor, slots: torch.Tensor, page_table: torch.Tensor,
                       k_cache: torch.Tensor, v_cache: torch.Tensor, *, keep_first: int = 0,
                       rel: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None, gate_stride: int = 0,
-                      precise: bool = False, chunk: int = 0, v_dim: int = 0) -> torch.Tensor:
+                      precise: bool = False, chunk: int = 0, v_dim: int = 0, sink: Optional[torch.Tensor] = None,
+                      v_share: int = 1) -> torch.Tensor:
     """bfloat16 causal attention of runs of new tokens on the tensor cores; block i handles up to 64
     new tokens of sequence tile_seq[i] from its row tile_row0[i] on.  ``keep_first``, ``rel`` and ``gate`` as
     for ``attention_general``; a value head may have a width of its own (``v_cache``'s rows; with ``precise``); ``precise``: the softmax weights enter the second product with 16 bits of
-    mantissa (as two bfloat16 terms) instead of 8.  ``chunk`` and ``v_cache`` None with ``v_dim`` as for
-    ``attention_general``."""
+    mantissa (as two bfloat16 terms) instead of 8.  ``chunk``, ``v_cache`` None with ``v_dim``, ``sink``, ``v_share``
+    and a float32 ``out`` as for ``attention_general``."""
     if not q.is_cuda or q.stride(-1) != 1 or q.dtype != torch.bfloat16:
         raise KernelError("attention_prefill: q must be a bfloat16 CUDA tensor with unit inner stride")
     v_row = 0
@@ -538,7 +634,16 @@ def attention_prefill(q: torch.Tensor, q_stride: int, out: torch.Tensor, n_heads
         v_cache, v_row, inner = k_cache, head_dim, v_dim
     else:
         inner = v_cache.shape[3]
-    _need(out, "out", torch.bfloat16, 2)
+    _need(out, "out", dims=2)
+    out_wide = out.dtype == torch.float32
+    if out.dtype not in (torch.bfloat16, torch.float32):
+        raise KernelError("attention_prefill: out must be bfloat16 or float32")
+    if v_share < 1 or n_kv_heads % v_share or (v_share > 1 and v_cache is None):
+        raise KernelError(f"attention_prefill: {n_kv_heads} key heads cannot share values {v_share} at a time")
+    if sink is not None:
+        _need(sink, "sink", torch.float32, 1)
+        if sink.shape[0] != n_heads:
+            raise KernelError(f"attention_prefill: {sink.shape[0]} sink scores for {n_heads} heads")
     for t, nm in ((tile_seq, "tile_seq"), (tile_row0, "tile_row0"), (seq_start, "seq_start"), (seq_pos0, "seq_pos0"),
                   (slots, "slots")):
         _need(t, nm, torch.int32, 1)
@@ -546,7 +651,8 @@ def attention_prefill(q: torch.Tensor, q_stride: int, out: torch.Tensor, n_heads
     _need(k_cache, "k_cache", torch.bfloat16, 4)
     _need(v_cache, "v_cache", torch.bfloat16, 4)
     v_dim = inner
-    if tuple(k_cache.shape[1:]) != (n_kv_heads, PAGE, head_dim) or tuple(k_cache.shape[:3]) != tuple(v_cache.shape[:3]):
+    if (tuple(k_cache.shape[1:]) != (n_kv_heads, PAGE, head_dim)
+            or tuple(v_cache.shape[:3]) != (k_cache.shape[0], n_kv_heads // v_share, PAGE)):
         raise KernelError(f"attention_prefill: cache {tuple(k_cache.shape)} / {tuple(v_cache.shape)} is not "
                           f"[pages, {n_kv_heads}, {PAGE}, {head_dim} / value width]")
     if head_dim % 16 or head_dim > 256 or n_heads % n_kv_heads or v_dim % 16 or v_dim > 256:
@@ -564,13 +670,14 @@ def attention_prefill(q: torch.Tensor, q_stride: int, out: torch.Tensor, n_heads
     if gate is not None and (not gate.is_cuda or gate.dtype != torch.bfloat16 or gate.stride(-1) != 1
                              or gate.shape[-1] < n_heads or gate_stride <= 0):
         raise KernelError("attention_prefill: gate must be a bfloat16 CUDA view with unit inner stride and one number per head")
-    if keep_first or rel is not None or gate is not None or precise or chunk or v_row:
+    if keep_first or rel is not None or gate is not None or precise or chunk or v_row or sink is not None or v_share > 1 or out_wide:
         _check(_fn("attention_prefill", "bn_attention_prefill_ex")(
             _ptr(q), int(q_stride), _ptr(out), int(out.shape[1]), int(tile_seq.shape[0]), int(n_heads),
             int(n_kv_heads), int(head_dim), int(v_dim), c_float(scale), int(window), int(keep_first), int(chunk), int(v_row),
             _ptr(rel), int(n_rel), _ptr(gate),
             int(gate_stride), int(bool(precise)), _ptr(tile_seq), _ptr(tile_row0), _ptr(seq_start), _ptr(seq_pos0), _ptr(slots),
-            _ptr(page_table), int(page_table.shape[1]), _ptr(k_cache), _ptr(v_cache), _stream()), "attention_prefill")
+            _ptr(page_table), int(page_table.shape[1]), _ptr(k_cache), _ptr(v_cache), _ptr(sink), int(v_share), int(out_wide),
+            _stream()), "attention_prefill")
         return out
     _check(_fn("attention_prefill", "bn_attention_prefill")(
         _ptr(q), int(q_stride), _ptr(out), int(out.shape[1]), int(tile_seq.shape[0]), int(n_heads),
@@ -592,7 +699,16 @@ def attention_prefill_tc(q: torch.Tensor, q_stride: int, out: torch.Tensor, n_he
     Head sizes up to 128."""
     if not q.is_cuda or q.dim() != 2 or q.stride(-1) != 1 or q.stride(0) != q_stride or q.dtype != torch.bfloat16:
         raise KernelError("attention_prefill_tc: q must be a bfloat16 CUDA matrix with unit inner stride")
-    _need(out, "out", torch.bfloat16, 2)
+    _need(out, "out", dims=2)
+    out_wide = out.dtype == torch.float32
+    if out.dtype not in (torch.bfloat16, torch.float32):
+        raise KernelError("attention_prefill: out must be bfloat16 or float32")
+    if v_share < 1 or n_kv_heads % v_share or (v_share > 1 and v_cache is None):
+        raise KernelError(f"attention_prefill: {n_kv_heads} key heads cannot share values {v_share} at a time")
+    if sink is not None:
+        _need(sink, "sink", torch.float32, 1)
+        if sink.shape[0] != n_heads:
+            raise KernelError(f"attention_prefill: {sink.shape[0]} sink scores for {n_heads} heads")
     for t, nm in ((tile_seq, "tile_seq"), (tile_row0, "tile_row0"), (seq_start, "seq_start"), (seq_pos0, "seq_pos0"),
                   (slots, "slots")):
         _need(t, nm, torch.int32, 1)
@@ -1258,8 +1374,9 @@ def rotary_pairs_append(x: torch.Tensor, freqs: torch.Tensor, tok_pos: torch.Ten
                         tok_seq: Optional[torch.Tensor] = None, slots: Optional[torch.Tensor] = None,
                         page_table: Optional[torch.Tensor] = None, k_cache: Optional[torch.Tensor] = None,
                         v_cache: Optional[torch.Tensor] = None, norm_len: int = 0, norm_w: Optional[torch.Tensor] = None,
-                        norm_eps: float = 0.0) -> None:
-    """Rotary encoding in the interleaved pairing, in place: in every row of x the pairs (2i, 2i + 1), i < len(freqs),
+                        norm_eps: float = 0.0, split_halves: bool = False, magnitude: float = 1.0) -> None:
+    """Rotary encoding in place: in every row of x the pairs (2i, 2i + 1), i < len(freqs) (with ``split_halves``
+    the pairs (i, i + len(freqs)); cos and sin both times ``magnitude``),
     of the rotated part of each query head (heads ``q_head_stride`` apart from ``q_off``, the part at ``q_rot_off``
     inside a head) and of each key head (likewise) are turned by ``tok_pos * freqs[i]``.  With a cache the first
     ``k_row`` numbers of every key head go there after rotation, and (``v_cache``) the first ``v_row`` numbers of
@@ -1301,7 +1418,7 @@ def rotary_pairs_append(x: torch.Tensor, freqs: torch.Tensor, tok_pos: torch.Ten
         int(n_q_heads), int(q_head_stride), int(q_rot_off), int(k_off), int(n_k_heads), int(k_head_stride), int(k_rot_off),
         int(k_row), int(v_off), int(v_head_stride), int(v_row), _ptr(tok_seq), _ptr(slots), _ptr(page_table), int(pt_stride),
         _ptr(k_cache), _ptr(v_cache), int(norm_len), _ptr(norm_w), int(_code(norm_w)) if norm_w is not None else 0,
-        c_float(norm_eps), _stream()), "rotary_pairs_append")
+        c_float(norm_eps), int(bool(split_halves)), c_float(magnitude), _stream()), "rotary_pairs_append")
 
 
 def residual_add(x: torch.Tensor, a: torch.Tensor, b: Optional[torch.Tensor] = None,
@@ -1534,6 +1651,22 @@ def moe_route(h: torch.Tensor, w_router: torch.Tensor, top: int, renormalise: bo
                                          int(_code(w_router)), int(w_router.shape[0]), int(top), int(bool(renormalise)),
                                          int(bool(softmax)), c_float(weight_scale), c_float(sum_eps), _ptr(ids), _ptr(weights),
                                          _stream()), "moe_route")
+    return ids, weights
+
+
+def moe_table_route(tokens: torch.Tensor, table: torch.Tensor, top: int, n_experts: int):
+    """Experts by token id: ``(ids int32 [T, top], weights float32 [T, top])`` with ids = ``table[token, :top]`` and
+    every weight 1 / top (an id or an entry out of range takes weight 0)."""
+    _need(tokens, "tokens", torch.int32, 1)
+    _need(table, "table", torch.int32, 2)
+    if not 0 < top <= table.shape[1]:
+        raise KernelError(f"moe_table_route: a table of {table.shape[1]} columns has no {top} experts per token")
+    T = tokens.shape[0]
+    ids = torch.empty((T, top), dtype=torch.int32, device=tokens.device)
+    weights = torch.empty((T, top), dtype=torch.float32, device=tokens.device)
+    _check(_fn("moe", "bn_moe_table_route")(_ptr(tokens), int(T), _ptr(table), int(table.shape[0]), int(table.shape[1]), int(top),
+                                            int(n_experts), c_float(1.0 / top), _ptr(ids), _ptr(weights), _stream()),
+           "moe_table_route")
     return ids, weights
 
 

@@ -1,8 +1,9 @@
-// Rotary position encoding in the interleaved pairing, with a table of frequencies, fused with the
-// write of the new keys (and values) into the paged cache.
+// Rotary position encoding with a table of frequencies, fused with the write of the new keys (and
+// values) into the paged cache.
 //
-// Dimension 2i of the rotated part of a head is paired with dimension 2i + 1; at position p the
-// pair (u, v) becomes (u cos a - v sin a, v cos a + u sin a) with a = p * freq[i] in float32.  The
+// Dimension 2i of the rotated part of a head is paired with dimension 2i + 1 (or, with split_halves,
+// dimension i with dimension i + half); at position p the pair (u, v) becomes
+// (u cos a - v sin a, v cos a + u sin a) with a = p * freq[i] in float32, cos and sin both times `magnitude`.  The
 // frequencies come as a table, so that whoever builds it decides base, scaling of long
 // wavelengths and the like (parts/position.py).  The rotated part may lie anywhere inside a head
 // (rot_off), so heads of the form [plain | rotated] and keys whose last numbers are a rotated part
@@ -27,7 +28,7 @@ __global__ void rotary_pairs_append_kernel(T* xq, int q_row_stride, T* xk, int r
                                            const int* __restrict__ tok_seq, const int* __restrict__ slots,
                                            const int* __restrict__ page_table, int pt_stride, T* __restrict__ k_cache,
                                            T* __restrict__ v_cache, int norm_len, const void* __restrict__ norm_w,
-                                           int norm_w_dtype, float norm_eps) {
+                                           int norm_w_dtype, float norm_eps, int split_halves, float magnitude) {
   pdl_launch_dependents();
   pdl_wait();
   __shared__ float cs[RP_MAX_HALF], sn[RP_MAX_HALF];
@@ -36,7 +37,12 @@ __global__ void rotary_pairs_append_kernel(T* xq, int q_row_stride, T* xk, int r
   const int pos = tok_pos[t];
   T* row = xk + (size_t)t * row_stride;    // the row that holds the key (and value) heads
   T* qrow = xq + (size_t)t * q_row_stride;  // the row that holds the query heads (may be the same)
-  for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf((float)pos * freqs[i], &sn[i], &cs[i]);
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    float sv, cv;
+    sincosf((float)pos * freqs[i], &sv, &cv);
+    sn[i] = sv * magnitude;
+    cs[i] = cv * magnitude;
+  }
   const int* pt = k_cache ? page_table + (size_t)slots[tok_seq[t]] * pt_stride : nullptr;
   if (norm_len > 0) {
     float ss = 0.f;
@@ -62,10 +68,13 @@ __global__ void rotary_pairs_append_kernel(T* xq, int q_row_stride, T* xk, int r
     const bool is_q = item < n_q;
     const int it = is_q ? item : item - n_q;
     const int h = it / half, i = it - h * half;
-    T* p = (is_q ? qrow + q_off + h * q_head_stride + q_rot_off : row + k_off + h * k_head_stride + k_rot_off) + 2 * i;
-    const float u = to_f32<T>(p[0]), v = to_f32<T>(p[1]), c = cs[i], s = sn[i];
-    p[0] = from_f32<T>(u * c - v * s);
-    p[1] = from_f32<T>(v * c + u * s);
+    T* p = (is_q ? qrow + q_off + h * q_head_stride + q_rot_off : row + k_off + h * k_head_stride + k_rot_off);
+    // the pair's two numbers: neighbours (2i, 2i + 1), or number i of the first half with number i of the second
+    T* pu = p + (split_halves ? i : 2 * i);
+    T* pv = p + (split_halves ? i + half : 2 * i + 1);
+    const float u = to_f32<T>(*pu), v = to_f32<T>(*pv), c = cs[i], s = sn[i];
+    *pu = from_f32<T>(u * c - v * s);
+    *pv = from_f32<T>(v * c + u * s);
   }
   if (!k_cache) return;
   __syncthreads();
@@ -87,7 +96,7 @@ extern "C" int bn_rotary_pairs_append(void* xq, int q_row_stride, void* xk, int 
                                       int v_head_stride, int v_row, const int* tok_seq, const int* slots,
                                       const int* page_table, int pt_stride, void* k_cache, void* v_cache,
                                       int norm_len, const void* norm_w, int norm_w_dtype, float norm_eps,
-                                      cudaStream_t stream) {
+                                      int split_halves, float magnitude, cudaStream_t stream) {
   if (n <= 0) return BN_OK;
   if (norm_len < 0 || (norm_len > 0 && (!norm_w || n_k_heads != 1 || norm_len > k_rot_off || !(norm_eps > 0.f) ||
                                         (norm_w_dtype != BN_F32 && norm_w_dtype != BN_BF16))))
@@ -104,13 +113,14 @@ extern "C" int bn_rotary_pairs_append(void* xq, int q_row_stride, void* xk, int 
   if (dtype == BN_F32)
     BN_LAUNCH(rotary_pairs_append_kernel<float>, n, RP_THREADS, 0, stream, (float*)xq, q_row_stride, (float*)xk, row_stride, freqs, half, tok_pos, q_off,
               n_q_heads, q_head_stride, q_rot_off, k_off, n_k_heads, k_head_stride, k_rot_off, k_row, v_off, v_head_stride,
-              v_row, tok_seq, slots, page_table, pt_stride, (float*)k_cache, (float*)v_cache, norm_len, norm_w, norm_w_dtype, norm_eps);
+              v_row, tok_seq, slots, page_table, pt_stride, (float*)k_cache, (float*)v_cache, norm_len, norm_w, norm_w_dtype, norm_eps,
+              split_halves, magnitude);
   else if (dtype == BN_BF16)
     BN_LAUNCH(rotary_pairs_append_kernel<__nv_bfloat16>, n, RP_THREADS, 0, stream, (__nv_bfloat16*)xq, q_row_stride,
               (__nv_bfloat16*)xk, row_stride, freqs, half,
               tok_pos, q_off, n_q_heads, q_head_stride, q_rot_off, k_off, n_k_heads, k_head_stride, k_rot_off, k_row, v_off,
               v_head_stride, v_row, tok_seq, slots, page_table, pt_stride, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, norm_len,
-              norm_w, norm_w_dtype, norm_eps);
+              norm_w, norm_w_dtype, norm_eps, split_halves, magnitude);
   else
     return BN_ERR_BAD_ARG;
   return BN_OK;

@@ -154,3 +154,158 @@ extern "C" int bn_slice_norm_append(void* x, int dtype, int n_tokens, int row_st
   BN_CHECK_LAUNCH();
   return BN_OK;
 }
+
+// Queries, keys and values of a token from the float32 rows of their projection: a bias added, RMS norms with gains
+// over spans of the query slice and of the key slice, a factor on the queries that grows with the position, the
+// row written out in the compute type, keys and values into the paged cache.
+//
+//   r = src + bias                                                     (float32)
+//   q_j <- q_j / sqrt(mean over its span (q^2) + eps) * wq[j mod q_span] * (1 + coef ln(floor((p + 1) / every) + 1))
+//   k_j <- k_j / sqrt(mean over its span (k^2) + eps) * wk[j mod k_span]
+//
+// A span of head_dim numbers norms every head by itself with one gain for all heads; a span of the whole slice
+// norms all heads of a token at once.  Span 0: no norm.  every 0: no factor.  The value plane may have fewer heads
+// than the key plane (n_v_heads).  One block per token; the row waits in shared memory between the phases.
+template <typename T>
+__global__ void qk_norm_append_kernel(const float* __restrict__ src, int src_stride, const void* __restrict__ bias, int bias_dtype,
+                                      T* __restrict__ out, int out_stride, int row_len, int q_len, int q_span,
+                                      const void* __restrict__ wq, int k_off, int k_len, int k_span, const void* __restrict__ wk,
+                                      int w_dtype, float eps, float temp_coef, int temp_every, int v_off, int n_kv_heads,
+                                      int head_dim, int n_v_heads, int v_dim, const int* __restrict__ tok_seq,
+                                      const int* __restrict__ tok_pos, const int* __restrict__ slots,
+                                      const int* __restrict__ page_table, int pt_stride, T* __restrict__ k_cache,
+                                      T* __restrict__ v_cache) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ __align__(16) float qk_row[];  // row_len numbers, then one inverse root mean square per span
+  float* inv = qk_row + row_len;
+  const int t = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+  const float* s = src + (size_t)t * src_stride;
+  for (int i = threadIdx.x; i < row_len; i += blockDim.x) qk_row[i] = s[i] + (bias ? load_as_f32(bias, bias_dtype, i) : 0.f);
+  __syncthreads();
+  const int nq = q_span > 0 ? q_len / q_span : 0, nk = k_span > 0 ? k_len / k_span : 0;
+  for (int g = warp; g < nq + nk; g += n_warps) {
+    const bool is_k = g >= nq;
+    const int span = is_k ? k_span : q_span;
+    const float* p = qk_row + (is_k ? k_off + (g - nq) * k_span : g * q_span);
+    float ss = 0.f;
+    for (int d = lane; d < span; d += 32) ss = fmaf(p[d], p[d], ss);
+    ss = warp_sum(ss);
+    if (lane == 0) inv[g] = 1.0f / sqrtf(ss / (float)span + eps);
+  }
+  __syncthreads();
+  const int pos = tok_pos[t];
+  const float temp = temp_every > 0 ? 1.0f + temp_coef * logf((float)((pos + 1) / temp_every) + 1.0f) : 1.0f;
+  const int* pt = k_cache ? page_table + (size_t)slots[tok_seq[t]] * pt_stride : nullptr;
+  T* o = out + (size_t)t * out_stride;
+  const int v_len = n_v_heads * v_dim;
+  for (int i = threadIdx.x; i < row_len; i += blockDim.x) {
+    float a = qk_row[i];
+    if (i < q_len) {
+      if (q_span > 0) a = a * inv[i / q_span] * load_as_f32(wq, w_dtype, i % q_span);
+      a *= temp;
+      o[i] = from_f32<T>(a);
+    } else if (i >= k_off && i < k_off + k_len) {
+      const int j = i - k_off;
+      if (k_span > 0) a = a * inv[nq + j / k_span] * load_as_f32(wk, w_dtype, j % k_span);
+      const T y = from_f32<T>(a);
+      o[i] = y;
+      if (k_cache) {
+        const int kvh = j / head_dim, d = j - kvh * head_dim;
+        k_cache[cache_row_offset(pt, pos, n_kv_heads, kvh, head_dim) + d] = y;
+      }
+    } else {
+      const T y = from_f32<T>(a);
+      o[i] = y;
+      if (v_cache && i >= v_off && i < v_off + v_len) {
+        const int j = i - v_off, vh = j / v_dim, d = j - vh * v_dim;
+        v_cache[cache_row_offset(pt, pos, n_v_heads, vh, v_dim) + d] = y;
+      }
+    }
+  }
+}
+
+extern "C" int bn_qk_norm_append(const float* src, int src_stride, const void* bias, int bias_dtype, void* out, int dtype, int out_stride,
+                                 int n_tokens, int row_len, int q_len, int q_span, const void* wq, int k_off, int k_len, int k_span,
+                                 const void* wk, int w_dtype, float eps, float temp_coef, int temp_every, int v_off, int n_kv_heads,
+                                 int head_dim, int n_v_heads, int v_dim, const int* tok_seq, const int* tok_pos, const int* slots,
+                                 const int* page_table, int pt_stride, void* k_cache, void* v_cache, cudaStream_t stream) {
+  if (n_tokens <= 0) return BN_OK;
+  if (!src || !out || !tok_pos || row_len <= 0 || row_len > src_stride || row_len > out_stride || q_len < 0 || k_len < 0 ||
+      q_len > k_off || k_off + k_len > row_len || q_span < 0 || k_span < 0 || (q_span > 0 && (!wq || q_len % q_span)) ||
+      (k_span > 0 && (!wk || k_len % k_span)) || !(eps > 0.f) || temp_every < 0 ||
+      (k_cache && (!v_cache || !tok_seq || !slots || !page_table || n_kv_heads <= 0 || head_dim <= 0 || n_v_heads <= 0 || v_dim <= 0 ||
+                   k_len != n_kv_heads * head_dim || v_off < k_off + k_len || v_off + n_v_heads * v_dim > row_len)))
+    return BN_ERR_BAD_ARG;
+  const int spans = (q_span > 0 ? q_len / q_span : 0) + (k_span > 0 ? k_len / k_span : 0);
+  const size_t smem = ((size_t)row_len + spans) * sizeof(float);
+  if (smem > 200 * 1024) return BN_ERR_BAD_ARG;
+#define BN_QK_PREP(TT)                                                                                                         \
+  do {                                                                                                                         \
+    if (smem > 48 * 1024) {                                                                                                    \
+      static size_t granted = 0;                                                                                               \
+      if (smem > granted) {                                                                                                    \
+        cudaError_t e = cudaFuncSetAttribute(qk_norm_append_kernel<TT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        if (e != cudaSuccess) return BN_ERR_LAUNCH + (int)e;                                                                   \
+        granted = smem;                                                                                                        \
+      }                                                                                                                        \
+    }                                                                                                                          \
+    BN_LAUNCH(qk_norm_append_kernel<TT>, n_tokens, UN_THREADS, smem, stream, src, src_stride, bias, bias_dtype, (TT*)out,      \
+              out_stride, row_len, q_len, q_span, wq, k_off, k_len, k_span, wk, w_dtype, eps, temp_coef, temp_every, v_off,    \
+              n_kv_heads, head_dim, n_v_heads, v_dim, tok_seq, tok_pos, slots, page_table, pt_stride, (TT*)k_cache,            \
+              (TT*)v_cache);                                                                                                   \
+  } while (0)
+  if (dtype == BN_F32) BN_QK_PREP(float);
+  else if (dtype == BN_BF16) BN_QK_PREP(__nv_bfloat16);
+  else return BN_ERR_BAD_ARG;
+#undef BN_QK_PREP
+  BN_CHECK_LAUNCH();
+  return BN_OK;
+}
+
+// Two maps of attention over the same values, combined: per token and head
+//   o = a1 - lambda a2;   o <- o / sqrt(mean(o^2) + eps) * post
+// a1 and a2 are float32 rows of v_dim numbers; the maps of the heads that share a key/value head lie as
+// [group][map][head in group][v_dim] in a row of `in`.  One warp per (token, head).
+template <typename T>
+__global__ void diff_combine_kernel(const float* __restrict__ in, int in_stride, T* __restrict__ out, int out_stride, int n_tokens,
+                                    int n_heads, int per_group, int v_dim, float lambda, float eps, float post) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int item = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (item >= n_tokens * n_heads) return;
+  const int t = item / n_heads, h = item - t * n_heads;
+  const int g = h / per_group, hg = h - g * per_group;
+  const float* a1 = in + (size_t)t * in_stride + ((size_t)(2 * g) * per_group + hg) * v_dim;
+  const float* a2 = a1 + (size_t)per_group * v_dim;
+  float ss = 0.f;
+  for (int d = lane; d < v_dim; d += 32) {
+    const float o = a1[d] - lambda * a2[d];
+    ss = fmaf(o, o, ss);
+  }
+  ss = warp_sum(ss);
+  const float scale = post / sqrtf(ss / (float)v_dim + eps);
+  T* orow = out + (size_t)t * out_stride + (size_t)h * v_dim;
+  for (int d = lane; d < v_dim; d += 32) orow[d] = from_f32<T>((a1[d] - lambda * a2[d]) * scale);
+}
+
+extern "C" int bn_diff_combine(const float* in, int in_stride, void* out, int dtype, int out_stride, int n_tokens, int n_heads,
+                               int per_group, int v_dim, float lambda, float eps, float post, cudaStream_t stream) {
+  if (n_tokens <= 0) return BN_OK;
+  if (!in || !out || n_heads <= 0 || per_group <= 0 || n_heads % per_group || v_dim <= 0 || !(eps > 0.f) ||
+      in_stride < 2 * n_heads * v_dim || out_stride < n_heads * v_dim)
+    return BN_ERR_BAD_ARG;
+  const long long items = (long long)n_tokens * n_heads;
+  const unsigned blocks = (unsigned)((items + 7) / 8);
+  if (dtype == BN_F32)
+    BN_LAUNCH(diff_combine_kernel<float>, blocks, 256, 0, stream, in, in_stride, (float*)out, out_stride, n_tokens, n_heads, per_group,
+              v_dim, lambda, eps, post);
+  else if (dtype == BN_BF16)
+    BN_LAUNCH(diff_combine_kernel<__nv_bfloat16>, blocks, 256, 0, stream, in, in_stride, (__nv_bfloat16*)out, out_stride, n_tokens,
+              n_heads, per_group, v_dim, lambda, eps, post);
+  else
+    return BN_ERR_BAD_ARG;
+  BN_CHECK_LAUNCH();
+  return BN_OK;
+}

@@ -53,6 +53,8 @@ class Model:
         b = BuildContext(dtype=self.dtype, device=self.device)
         self.blocks = [build_part("block", bs, b) for bs in spec.blocks]
         self.final_norm = build_part("norm", spec.final_norm, b)
+        en = getattr(spec, "embedding_norm", None)
+        self.embedding_norm = build_part("norm", en, b) if en is not None else None
         self.head_part = build_part("head", spec.head, b)
         self.embedding: Optional[torch.Tensor] = None
         self.head: Optional[torch.Tensor] = None
@@ -60,7 +62,10 @@ class Model:
         self.diagnostics = None  # engine/diagnostics.py: tensor dumps, top logits, kernel timers
         self._owners: Dict[str, tuple] = {}
         for i, blk in enumerate(self.blocks):
-            _walk(f"blocks.{i}", blk, self._owners)
+            # a block's parameters are listed under its index, or under the label its spec gives it
+            _walk(f"blocks.{getattr(spec.blocks[i], 'label', None) or i}", blk, self._owners)
+        if self.embedding_norm is not None:
+            _walk("embedding_norm", self.embedding_norm, self._owners)
         _walk("final_norm", self.final_norm, self._owners)
         _walk("head", self.head_part, self._owners)  # a head's own parameters; the matrix is "head.weight"
         if "head.weight" in self._owners:
@@ -81,7 +86,8 @@ class Model:
         be recorded once and replayed (parts say so with ``graph_safe = True``)."""
         def ok(part) -> bool:
             return bool(getattr(part, "graph_safe", False)) and all(ok(c) for c in part.children().values())
-        return all(ok(b) for b in self.blocks) and ok(self.final_norm) and ok(self.head_part)
+        return (all(ok(b) for b in self.blocks) and ok(self.final_norm) and ok(self.head_part)
+                and (self.embedding_norm is None or ok(self.embedding_norm)))
 
     def decode_blocks_per_sequence(self) -> int:
         """The most thread blocks any part launches per sequence in a decode step (0: no part takes
@@ -93,6 +99,8 @@ class Model:
         for blk in self.blocks:
             fams.extend(blk.all_kernels())
         fams.extend(self.final_norm.all_kernels())
+        if self.embedding_norm is not None:
+            fams.extend(self.embedding_norm.all_kernels())
         fams.extend(self.head_part.all_kernels())
         return list(dict.fromkeys(fams))
 
@@ -229,6 +237,8 @@ class Model:
         """Embedding, every scheduled run, final norm and head at the wanted rows."""
         x = torch.empty((ctx.n_tokens, self.spec.width), dtype=torch.float32, device=self.device)
         ops.embed_gather(self.embedding, ctx.tokens, x, self._bad_token, self.spec.embedding_scale)
+        if self.embedding_norm is not None:  # the stream starts as the normed embedding rows
+            ops.scaled_add_rmsnorm(x, 1.0, None, self.embedding_norm.weight, self.embedding_norm.spec.eps)
         diag = ctx.diag = self.diagnostics
         ctx.layer = -1
         ctx.tap("inp", x)

@@ -42,8 +42,11 @@ class ParamSpec:
     """A parameter of a part: its shape, how random weights fill it, whether it is an integer table."""
 
     shape: Tuple[int, ...]
-    init: str = "normal"  # "normal": N(0, std) matrix; "ones": gain around 1; "zeros"
+    # "normal": N(0, std) matrix; "ones": gain around 1; "around_zero": gain stored as its distance from 1; "zeros";
+    # "distinct": integer rows of different numbers below ``high``
+    init: str = "normal"
     integer: bool = False
+    high: int = 0
     # a tensor the file may lack (a bias, an extra norm): the part is then bound with None for it,
     # as the reference treats such tensors as "present or NULL" (src/model.c:525-913)
     optional: bool = False
@@ -63,7 +66,7 @@ class KvRequest:
     are cut into chunks of so many and only those of the chunk a sequence is in are kept.
     ``values_in_keys``: the values are a part of the key rows, so the group has no value plane.
     ``v_head_dim``: the width of a value head when it differs from a key head's (0: the same).
-    The library's attention kernels take equal widths; a mixer with others brings its own."""
+    ``v_heads``: the number of value heads when several key heads read one value head (0: as many as key heads)."""
 
     n_kv_heads: int
     head_dim: int
@@ -72,10 +75,15 @@ class KvRequest:
     keep_first: int = 0
     chunk: int = 0
     values_in_keys: bool = False
+    v_heads: int = 0
 
     @property
     def v_dim(self) -> int:
         return self.v_head_dim or self.head_dim
+
+    @property
+    def n_v_heads(self) -> int:
+        return self.v_heads or self.n_kv_heads
 
 
 @dataclass(frozen=True)

@@ -194,3 +194,66 @@ class ParallelBlock(Block):
             ops.add_normed(x, y, self.side.gain, s.eps)
             return None
         return Normed(ops.add_normed(x, y, self.side.gain, s.eps, fused.weight, fused.spec.eps, self.build.dtype))
+
+
+@register_block("sandwich")
+class SandwichBlock(Block):
+    """x <- x + post(mixer(pre(x))); x <- x + ffn_post(ffn(ffn_pre(x))): a norm before and after each sublayer.
+    The sublayers leave their products in float32; one pass divides a sublayer's output by its root mean square,
+    multiplies by the gain, adds it to the float32 stream and takes the norm that reads the new rows next (this
+    block's second pre-norm, or the next block's first when that reader says which it is).  Without a feed-forward
+    the second step is left out."""
+
+    graph_safe = True  # as far as its parts are
+    accepts_normed = True
+
+    def __init__(self, spec, build):
+        super().__init__(spec, build)
+        self.mixer_norm = build_part("norm", spec.mixer_norm, build)
+        self.mixer = build_part("mixer", spec.mixer, build)
+        self.mixer_post_norm = build_part("norm", spec.mixer_post_norm, build)
+        self.ffn = build_part("ffn", spec.ffn, build) if spec.ffn is not None else None
+        if self.ffn is not None and (spec.ffn_norm is None or spec.ffn_post_norm is None):
+            raise ValueError("a sandwich block with a feed-forward needs both of its norms")
+        self.ffn_norm = build_part("norm", spec.ffn_norm, build) if self.ffn is not None else None
+        self.ffn_post_norm = build_part("norm", spec.ffn_post_norm, build) if self.ffn is not None else None
+
+    def children(self):
+        c = {"mixer_norm": self.mixer_norm, "mixer": self.mixer, "mixer_post_norm": self.mixer_post_norm}
+        if self.ffn is not None:
+            c.update(ffn_norm=self.ffn_norm, ffn=self.ffn, ffn_post_norm=self.ffn_post_norm)
+        return c
+
+    def entry_norm(self):
+        return self.mixer_norm
+
+    def cache_request(self):
+        return self.mixer.cache_request()
+
+    def state_request(self):
+        return self.mixer.state_request()
+
+    def _add(self, x, y, post, reader):
+        """x += post(y); the reader's norm of the new rows, if there is a reader whose gain is at hand."""
+        w = getattr(reader, "weight", None) if reader is not None else None
+        if w is None:
+            ops.add_normed(x, y, post.weight, post.spec.eps)
+            return None
+        return ops.add_normed(x, y, post.weight, post.spec.eps, w, reader.spec.eps, self.build.dtype)
+
+    def forward(self, x, pending, ctx, kv, state, next_norm=None):
+        if isinstance(pending, Normed):
+            h = pending.value.dense() if isinstance(pending.value, ops.RowScaled) else pending.value
+        else:
+            h = self.mixer_norm.add_norm(x, pending, ctx)
+        ctx.tap("attn_norm", h)
+        d = self.mixer.forward(h, ctx, kv, state)
+        ctx.tap("attn_proj", d)
+        h = self._add(x, d, self.mixer_post_norm, self.ffn_norm if self.ffn is not None else next_norm)
+        if self.ffn is None:
+            return Normed(h) if h is not None else None
+        ctx.tap("ffn_norm", h)
+        f = self.ffn.forward(h, ctx)
+        ctx.tap("ffn_out", f)
+        h = self._add(x, f, self.ffn_post_norm, next_norm)
+        return Normed(h) if h is not None else None

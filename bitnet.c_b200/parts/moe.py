@@ -19,7 +19,8 @@ class Moe(FeedForward):
     limit of its own) runs for every token and is added.  By the spec: ``scores`` "softmax" takes the softmax
     over all experts as scores; ``renormalise`` divides the chosen ones' by their sum (+ ``renormalise_eps``);
     ``weight_scale`` multiplies the weights; ``activation`` "silu" / "gelu_tanh" makes an expert
-    down(act(gate x) * (up x)) without clamps.
+    down(act(gate x) * (up x)) without clamps; ``scores`` "table": no router, a table of expert ids by token id
+    chooses and every chosen expert weighs 1 / top.
 
     Few rows (a decode step): two kernels stream the chosen experts once per (token, expert), from
     device memory alone.  Many rows: the (token, expert) items are sorted by expert and every expert's
@@ -33,8 +34,11 @@ class Moe(FeedForward):
     def __init__(self, spec, build):
         super().__init__(spec, build)
         scores, activation = getattr(spec, "scores", "sigmoid"), getattr(spec, "activation", "limited")
-        if scores not in ("sigmoid", "softmax"):
-            raise ValueError(f"router scores are 'sigmoid' or 'softmax', not {scores!r}")
+        if scores not in ("sigmoid", "softmax", "table"):
+            raise ValueError(f"router scores are 'sigmoid', 'softmax' or 'table', not {scores!r}")
+        self.by_table = scores == "table"
+        if self.by_table and (getattr(spec, "table_rows", 0) <= 0 or spec.shared_ff or spec.weight_on_input):
+            raise ValueError("experts chosen by a table need its number of rows, weigh their outputs and have no shared expert")
         if activation != "limited" and activation not in ops.ACTIVATIONS:
             raise ValueError(f"expert activation {activation!r} is not built; known: limited, {', '.join(sorted(ops.ACTIVATIONS))}")
         self.softmax = scores == "softmax"
@@ -51,7 +55,10 @@ class Moe(FeedForward):
 
     def params(self) -> Dict[str, ParamSpec]:
         s = self.spec
-        p = {"router": ParamSpec((s.n_experts, s.width))}
+        if self.by_table:  # token id -> the ids of its experts, different within a row
+            p = {"table": ParamSpec((s.table_rows, s.top), init="distinct", integer=True, high=s.n_experts)}
+        else:
+            p = {"router": ParamSpec((s.n_experts, s.width))}
         for e in range(s.n_experts):
             p[f"e{e}.gate"] = ParamSpec((s.expert_ff, s.width))
             p[f"e{e}.up"] = ParamSpec((s.expert_ff, s.width))
@@ -65,7 +72,8 @@ class Moe(FeedForward):
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         s = self.spec
         dt = self.build.dtype
-        self.w_router = tensors["router"]
+        self.w_router = tensors.get("router")
+        self.table = tensors.get("table")
         # [experts, 2 ff, width]: an expert's gate rows, then its up rows; [experts, width, ff]
         self.w_gate_up = torch.stack([torch.cat([tensors[f"e{e}.gate"].to(dt), tensors[f"e{e}.up"].to(dt)], dim=0)
                                       for e in range(s.n_experts)]).contiguous()
@@ -84,8 +92,11 @@ class Moe(FeedForward):
         s = self.spec
         T = h.shape[0]
         shared = self._expert(h, self.w_shared_gate_up, self.w_shared_down, s.shared_limit, torch.float32) if s.shared_ff else None
-        ids, weights = ops.moe_route(h, self.w_router, s.top, s.renormalise, softmax=self.softmax,
-                                     weight_scale=getattr(s, "weight_scale", 1.0), sum_eps=getattr(s, "renormalise_eps", 0.0))
+        if self.by_table:
+            ids, weights = ops.moe_table_route(ctx.tokens, self.table, s.top, s.n_experts)
+        else:
+            ids, weights = ops.moe_route(h, self.w_router, s.top, s.renormalise, softmax=self.softmax,
+                                         weight_scale=getattr(s, "weight_scale", 1.0), sum_eps=getattr(s, "renormalise_eps", 0.0))
         if ctx.diag is not None:
             ctx.tap("moe_ids", lambda: ids.float())
         if self.few_fits and (ctx.decode or T * s.top <= self.FEW_ITEMS):

@@ -19,10 +19,16 @@ class RmsNorm(Norm):
     graph_safe = True
 
     def params(self) -> Dict[str, ParamSpec]:
-        return {"weight": ParamSpec((self.spec.width,), init="ones", optional=bool(getattr(self.spec, "optional", False)))}
+        one_plus = bool(getattr(self.spec, "one_plus", False))
+        return {"weight": ParamSpec((self.spec.width,), init="around_zero" if one_plus else "ones",
+                                    optional=bool(getattr(self.spec, "optional", False)))}
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         self.weight = tensors["weight"]
+        if self.weight is not None and getattr(self.spec, "one_plus", False):
+            # a gain stored around zero: the factor 1 + w, made once in float32 (in bfloat16 the sum would lose the
+            # stored gain's low bits); the kernels read gains of either type
+            self.weight = (1.0 + self.weight.float()).contiguous()
 
     def sink(self, x, ctx):
         # a product in bfloat16 of few rows, or of many, can add to the residual and prepare this norm's output

@@ -93,3 +93,50 @@ class RotaryPairs(Position):
     def apply(self, x, ctx, **places):
         """``ops.rotary_pairs_append`` with this encoding's table and the step's positions."""
         ops.rotary_pairs_append(x, self.freqs(x.device), ctx.tok_pos, **places)
+
+
+def blended_frequencies(spec):
+    """(table, magnitude) of a ``RotaryBlendSpec``: base^(-2i/dims) for i < dims/2 in double precision, the slow
+    ones divided by ``factor`` along a ramp between the dimension that turns ``fast`` times within ``original``
+    positions and the one that turns ``slow`` times; rounded to float32 once.  The magnitude multiplies cos and
+    sin alike."""
+    dims = spec.dims
+    i = np.arange(dims // 2, dtype=np.float64)
+    f = np.float64(spec.base) ** (-2.0 * i / dims)
+    if spec.factor == 1.0 or spec.original <= 0:
+        return f.astype(np.float32), 1.0
+
+    def turns(t):
+        return dims * np.log(spec.original / (2.0 * np.pi * t)) / (2.0 * np.log(spec.base))
+
+    lo = max(int(np.floor(turns(spec.fast))), 0)
+    hi = min(int(np.ceil(turns(spec.slow))), dims - 1)
+    ramp = np.clip((i - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+    f = f / spec.factor * ramp + f * (1.0 - ramp)
+    return f.astype(np.float32), float(spec.magnitude_slope * np.log(spec.factor) + 1.0)
+
+
+@register_position("rotary_blend")
+class RotaryBlend(RotaryPairs):
+    """Rotary encoding over a table whose slow frequencies are divided by a factor along a ramp
+    (``blended_frequencies``), cos and sin both times a magnitude, in the halves pairing (number i of the rotated
+    part with number i + dims / 2) or the neighbours pairing.  The same kernel and the same ``rotate`` / ``apply``
+    as ``rotary_pairs``."""
+
+    def __init__(self, spec, build):
+        Position.__init__(self, spec, build)
+        if spec.dims % 2 or spec.dims <= 0 or spec.dims > 512:
+            raise ValueError(f"rotary dims={spec.dims} must be even and at most 512")
+        if spec.pairing not in ("halves", "neighbours"):
+            raise ValueError(f"rotary pairing is 'halves' or 'neighbours', not {spec.pairing!r}")
+        self._table, self.magnitude = blended_frequencies(spec)
+        self._freqs = None
+        self.split_halves = spec.pairing == "halves"
+
+    def rotate(self, x, n_heads, head_dim, ctx):
+        ops.rotary_pairs_append(x, self.freqs(x.device), ctx.tok_pos, q_off=0, n_q_heads=n_heads, q_head_stride=head_dim,
+                                split_halves=self.split_halves, magnitude=self.magnitude)
+
+    def apply(self, x, ctx, **places):
+        ops.rotary_pairs_append(x, self.freqs(x.device), ctx.tok_pos, split_halves=self.split_halves, magnitude=self.magnitude,
+                                **places)

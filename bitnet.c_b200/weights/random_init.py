@@ -131,6 +131,15 @@ def _draw(path, name, p, seed, dtype, matrix_std, norm_std, device):
         yield path, name, random_tensor(seed, name, p.shape, 1.0, norm_std, dtype, device)
     elif p.init == "normal":
         yield path, name, random_tensor(seed, name, p.shape, 0.0, matrix_std, dtype, device)
+    elif p.init == "around_zero":  # a gain that is stored as its distance from one
+        yield path, name, random_tensor(seed, name, p.shape, 0.0, norm_std, dtype, device)
+    elif p.init == "distinct":
+        # an integer table whose rows hold different numbers below ``p.high``: the first columns of a permutation
+        # that the seeded generator orders
+        rows, cols = p.shape
+        z = standard_normal(seed, name, rows * p.high).reshape(rows, p.high)
+        t = torch.from_numpy(np.argsort(z, axis=1, kind="stable")[:, :cols].astype(np.int32))
+        yield path, name, t if device is None else t.to(device)
     elif p.init == "zeros":
         yield path, name, torch.zeros(p.shape, dtype=torch.int32 if p.integer else dtype, device=device)
     else:
