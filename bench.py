@@ -520,6 +520,40 @@ MEKEVIK_SIZES = {
 }
 
 
+def netanex_sizes(width, heads, kv_heads, dim, vdim, rot_dim, kv_rank, window, ff, experts, top, vocab):
+    """A Netanex configuration of four layers (attention with whole-projection norms and a one in the softmax's
+    denominator; attention with two maps per head of half the head size each; latent attention under a window with
+    a learned sink; the first layer's weights once more with a cache of its own; every layer with experts chosen
+    by a table, a token's experts together as wide as the dense unit) and the Llama configuration of the same
+    width, heads, layers, vocabulary and feed-forward width."""
+    moe = {"kind": "moe", "router": {"experts": experts, "top": top}, "expert": {"ff": ff // top}}
+    whole = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": dim ** -0.5 * 4}
+    two = {"heads": heads, "kv_heads": kv_heads, "dim": dim // 2, "vdim": vdim, "scale": (dim // 2) ** -0.5 * 4, "diff": 0.6,
+           "q_temp": {"coef": 0.5, "every": 128}}
+    latent = {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": vdim, "kv_rank": kv_rank, "scale": (dim + rot_dim) ** -0.5,
+              "mask": {"size": window},
+              "rot": {"base": 1e6, "dims": rot_dim, "scaling": {"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0}}}
+    layers = [{"type": "attention_2", "mixer": whole, "mlp": moe}, {"type": "attention", "mixer": two, "mlp": moe},
+              {"type": "latent_attention", "mixer": latent, "mlp": moe},
+              {"type": "attention_2", "mixer": whole, "mlp": moe, "weights_of": 0}]
+    net = {"architecture": "Netanex", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "layers": layers, "max_positions": 8192}
+    llama = {"architectures": ["LlamaForCausalLM"], "model_type": "llama", "hidden_size": width, "intermediate_size": ff,
+             "num_hidden_layers": len(layers), "num_attention_heads": heads, "num_key_value_heads": kv_heads, "head_dim": dim,
+             "vocab_size": vocab, "max_position_embeddings": 8192, "rope_theta": 500000.0, "rms_norm_eps": 1e-5,
+             "tie_word_embeddings": True, "hidden_act": "silu"}
+    return net, llama
+
+
+NETANEX_SIZES = {
+    "w1024": dict(width=1024, heads=8, kv_heads=2, dim=128, vdim=128, rot_dim=64, kv_rank=192, window=1024, ff=4096, experts=8, top=2,
+                  vocab=32000),
+    "w2048": dict(width=2048, heads=16, kv_heads=4, dim=128, vdim=128, rot_dim=64, kv_rank=192, window=1024, ff=8192, experts=8, top=2,
+                  vocab=32000),
+    "w4096": dict(width=4096, heads=32, kv_heads=8, dim=128, vdim=128, rot_dim=64, kv_rank=512, window=1024, ff=14336, experts=8,
+                  top=2, vocab=32000),
+}
+
+
 def kernel_classes(model, vocab, tokens, batch, prompt_len):
     """Device time by entry point (ms) of one step of ``tokens`` prompt tokens and of one decode step of
     ``batch`` sequences behind prompts of ``prompt_len``, each kernel between two events (no graph, so the
@@ -560,7 +594,7 @@ def kernel_classes(model, vocab, tokens, batch, prompt_len):
 
 
 def run_design(args):
-    """``--design fesorax | lotilix | mekevik``: prefill and decode throughput of that design at layer sizes of real
+    """``--design fesorax | lotilix | mekevik | netanex``: prefill and decode throughput of that design at layer sizes of real
     models (random weights, bfloat16), beside the Llama decoder of equal width, heads, layers, vocabulary and
     feed-forward work per token, with each step's device time by kernel entry point."""
     import torch
@@ -570,6 +604,7 @@ def run_design(args):
            "dtype": "bf16", "data": "synthetic", "n_gpus": 1, "peaks": pk, "prefill_tokens": PREFILL_TOKENS,
            "decode_batch": args.batch, "decode_prompt": PROMPT_LEN, "sizes": {}}
     sizes, maker = {"lotilix": (LOTILIX_SIZES, lotilix_sizes), "mekevik": (MEKEVIK_SIZES, mekevik_sizes),
+                    "netanex": (NETANEX_SIZES, netanex_sizes),
                     "fesorax": (DESIGN_SIZES, fesorax_sizes)}[args.design]
     rec["metric"] = rec["metric"].replace("Fesorax", args.design.capitalize())
     names = [n for n in sizes if not args.sizes or n in args.sizes.split(",")]
@@ -610,7 +645,7 @@ def main():
                          "(comparisons, profiling)")
     ap.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16",
                     help="compute type of the main decode run (float32: profiling of the 32-bit path, with --skip-points)")
-    ap.add_argument("--design", choices=["fesorax", "lotilix", "mekevik"],
+    ap.add_argument("--design", choices=["fesorax", "lotilix", "mekevik", "netanex"],
                     help="measure another design of the library beside Llama at equal size instead (prefill, decode, "
                          "time by kernel); the default workload and its record stay as they are")
     ap.add_argument("--sizes", default="", help="with --design: which size sets, with commas (default: all)")

@@ -699,16 +699,7 @@ def attention_prefill_tc(q: torch.Tensor, q_stride: int, out: torch.Tensor, n_he
     Head sizes up to 128."""
     if not q.is_cuda or q.dim() != 2 or q.stride(-1) != 1 or q.stride(0) != q_stride or q.dtype != torch.bfloat16:
         raise KernelError("attention_prefill_tc: q must be a bfloat16 CUDA matrix with unit inner stride")
-    _need(out, "out", dims=2)
-    out_wide = out.dtype == torch.float32
-    if out.dtype not in (torch.bfloat16, torch.float32):
-        raise KernelError("attention_prefill: out must be bfloat16 or float32")
-    if v_share < 1 or n_kv_heads % v_share or (v_share > 1 and v_cache is None):
-        raise KernelError(f"attention_prefill: {n_kv_heads} key heads cannot share values {v_share} at a time")
-    if sink is not None:
-        _need(sink, "sink", torch.float32, 1)
-        if sink.shape[0] != n_heads:
-            raise KernelError(f"attention_prefill: {sink.shape[0]} sink scores for {n_heads} heads")
+    _need(out, "out", torch.bfloat16, 2)
     for t, nm in ((tile_seq, "tile_seq"), (tile_row0, "tile_row0"), (seq_start, "seq_start"), (seq_pos0, "seq_pos0"),
                   (slots, "slots")):
         _need(t, nm, torch.int32, 1)
