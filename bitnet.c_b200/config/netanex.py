@@ -117,8 +117,8 @@ class NetanexConfig:
             rot = _need(m, "rot", where)
             rot_dim = _int(m, "rot_dim", where)
             dims = _int(rot, "dims", where + ".rot")
-            if dims != rot_dim or dims % 2:
-                raise ConfigError(f"config.json: {where}.rot.dims={dims} must be even and equal rot_dim={rot_dim}")
+            if dims > rot_dim or dims % 2:  # the first rot.dims numbers of the rotated part turn, the rest pass unchanged
+                raise ConfigError(f"config.json: {where}.rot.dims={dims} must be even and at most rot_dim={rot_dim}")
             sc = rot.get("scaling") or None
             position = RotaryBlendSpec(dims=dims, base=_num(rot, "base", where + ".rot"),
                                        factor=_num(sc, "factor", where + ".rot.scaling") if sc else 1.0,
@@ -167,8 +167,10 @@ class NetanexConfig:
                 blocks.append(block)
                 schedule.append(ScheduleEntry(block=block_of[i]))
                 continue
-            if isinstance(j, bool) or not isinstance(j, int) or j not in block_of:
-                raise ConfigError(f"config.json: layers[{i}].weights_of={j!r} must name an earlier layer that has tensors of its own")
+            if isinstance(j, bool) or not isinstance(j, int) or not 0 <= j < i:
+                raise ConfigError(f"config.json: layers[{i}].weights_of={j!r} must name an earlier layer")
+            while d["layers"][j].get("weights_of") is not None:  # a layer that itself runs with another's weights
+                j = d["layers"][j]["weights_of"]
             other = blocks[block_of[j]]
             if (block.mixer, block.ffn) != (other.mixer, other.ffn):
                 raise ConfigError(f"config.json: layers[{i}] uses the weights of layer {j} but its mixer or feed-forward differs from that layer's")

@@ -121,6 +121,36 @@ def embed_gather(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor, b
     return out
 
 
+EMBED_NORMED_MAX_WIDTH = (200 * 1024) // 4 - 32  # rows that fit the fused kernel's shared memory
+
+
+def embed_gather_normed(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor, bad_token: torch.Tensor, scale: float,
+                        weight: torch.Tensor, eps: float, next_weight: Optional[torch.Tensor] = None, next_eps: float = 0.0,
+                        next_dtype: Optional[torch.dtype] = None) -> Optional[torch.Tensor]:
+    """out[t] = rmsnorm(float32(table[tokens[t]]) * scale) * weight: the stream starts as the normed embedding rows.
+    With ``next_weight`` also returns rmsnorm(out) * next_weight in ``next_dtype``: the first reader's norm, taken in
+    the same pass.  Sets bad_token[0] = 1 on an id outside the table (its rows are zeros)."""
+    _need(table, "table", dims=2)
+    _need(tokens, "tokens", torch.int32, 1)
+    _need(out, "out", torch.float32, 2)
+    _need(bad_token, "bad_token", torch.int32)
+    _need(weight, "weight", dims=1)
+    n, width = tokens.shape[0], table.shape[1]
+    if out.shape[0] < n or out.shape[1] != width or weight.shape[0] != width or width > EMBED_NORMED_MAX_WIDTH:
+        raise KernelError(f"embed_gather_normed: out {tuple(out.shape)} / gain {tuple(weight.shape)} do not fit {n} rows of width {width}")
+    h = None
+    if next_weight is not None:
+        _need(next_weight, "next_weight", dims=1)
+        if next_weight.shape[0] != width:
+            raise KernelError("embed_gather_normed: the reader's gain does not fit")
+        h = torch.empty((n, width), dtype=next_dtype or torch.float32, device=out.device)
+    _check(_fn("embed", "bn_embed_gather_normed")(
+        _ptr(table), _code(table), _ptr(tokens), _ptr(out), int(n), int(width), int(table.shape[0]), c_float(scale), _ptr(weight),
+        int(_code(weight)), c_float(eps), _ptr(next_weight), int(_code(next_weight)) if next_weight is not None else 0,
+        c_float(next_eps), _ptr(h), int(_code(h)) if h is not None else 0, _ptr(bad_token), _stream()), "embed_gather_normed")
+    return h
+
+
 # ---- norm ---------------------------------------------------------------------------------
 def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
                 out: torch.Tensor, rows: Optional[torch.Tensor] = None, write_x: bool = True) -> torch.Tensor:
@@ -421,18 +451,21 @@ def qk_norm_append(src: torch.Tensor, out: torch.Tensor, tok_pos: torch.Tensor, 
 
 
 def diff_combine(maps: torch.Tensor, out: torch.Tensor, n_heads: int, per_group: int, v_dim: int, lam: float, eps: float,
-                 post: float) -> torch.Tensor:
+                 post: float, tail: int = 0) -> torch.Tensor:
     """Two attention maps over the same values combined per token and head: o = a1 - ``lam`` a2, divided by its root
     mean square over the head's ``v_dim`` numbers (``eps`` inside the root), times ``post``.  ``maps`` is float32
     ``[n, 2 * n_heads * v_dim]`` with the maps of the ``per_group`` heads that share a key/value head laid out as
-    [group][map][head in group][v_dim]; ``out`` ``[n, n_heads * v_dim]`` holds the heads in their own order."""
+    [group][map][head in group][v_dim]; ``out`` ``[n, n_heads * v_dim + tail]`` holds the heads in their own order and
+    behind them a one and ``tail`` - 1 zeros (``tail`` > 0: the product that reads the rows then adds a bias that is
+    stored as a column of its matrix)."""
     _need(maps, "maps", torch.float32, 2)
     _need(out, "out", dims=2)
-    if maps.shape[1] != 2 * n_heads * v_dim or out.shape[1] != n_heads * v_dim or out.shape[0] < maps.shape[0] or n_heads % per_group:
+    if (maps.shape[1] != 2 * n_heads * v_dim or out.shape[1] != n_heads * v_dim + tail or out.shape[0] < maps.shape[0]
+            or n_heads % per_group or not 0 <= tail <= 32):
         raise KernelError("diff_combine: sizes do not fit")
     _check(_fn("unit_norm", "bn_diff_combine")(_ptr(maps), int(maps.stride(0)), _ptr(out), int(_code(out)), int(out.stride(0)),
                                                int(maps.shape[0]), int(n_heads), int(per_group), int(v_dim), c_float(lam),
-                                               c_float(eps), c_float(post), _stream()), "diff_combine")
+                                               c_float(eps), c_float(post), int(tail), _stream()), "diff_combine")
     return out
 
 

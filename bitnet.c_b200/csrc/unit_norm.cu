@@ -267,10 +267,12 @@ extern "C" int bn_qk_norm_append(const float* src, int src_stride, const void* b
 // Two maps of attention over the same values, combined: per token and head
 //   o = a1 - lambda a2;   o <- o / sqrt(mean(o^2) + eps) * post
 // a1 and a2 are float32 rows of v_dim numbers; the maps of the heads that share a key/value head lie as
-// [group][map][head in group][v_dim] in a row of `in`.  One warp per (token, head).
+// [group][map][head in group][v_dim] in a row of `in`.  One warp per (token, head).  tail > 0: behind the heads
+// every row of out gets a one and tail - 1 zeros, so that the product that reads the rows adds a bias that is
+// stored as a column of its matrix.
 template <typename T>
 __global__ void diff_combine_kernel(const float* __restrict__ in, int in_stride, T* __restrict__ out, int out_stride, int n_tokens,
-                                    int n_heads, int per_group, int v_dim, float lambda, float eps, float post) {
+                                    int n_heads, int per_group, int v_dim, float lambda, float eps, float post, int tail) {
   pdl_launch_dependents();
   pdl_wait();
   const int item = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
@@ -288,22 +290,23 @@ __global__ void diff_combine_kernel(const float* __restrict__ in, int in_stride,
   const float scale = post / sqrtf(ss / (float)v_dim + eps);
   T* orow = out + (size_t)t * out_stride + (size_t)h * v_dim;
   for (int d = lane; d < v_dim; d += 32) orow[d] = from_f32<T>((a1[d] - lambda * a2[d]) * scale);
+  if (h == 0 && lane < tail) out[(size_t)t * out_stride + (size_t)n_heads * v_dim + lane] = from_f32<T>(lane == 0 ? 1.f : 0.f);
 }
 
 extern "C" int bn_diff_combine(const float* in, int in_stride, void* out, int dtype, int out_stride, int n_tokens, int n_heads,
-                               int per_group, int v_dim, float lambda, float eps, float post, cudaStream_t stream) {
+                               int per_group, int v_dim, float lambda, float eps, float post, int tail, cudaStream_t stream) {
   if (n_tokens <= 0) return BN_OK;
-  if (!in || !out || n_heads <= 0 || per_group <= 0 || n_heads % per_group || v_dim <= 0 || !(eps > 0.f) ||
-      in_stride < 2 * n_heads * v_dim || out_stride < n_heads * v_dim)
+  if (!in || !out || n_heads <= 0 || per_group <= 0 || n_heads % per_group || v_dim <= 0 || !(eps > 0.f) || tail < 0 || tail > 32 ||
+      in_stride < 2 * n_heads * v_dim || out_stride < n_heads * v_dim + tail)
     return BN_ERR_BAD_ARG;
   const long long items = (long long)n_tokens * n_heads;
   const unsigned blocks = (unsigned)((items + 7) / 8);
   if (dtype == BN_F32)
     BN_LAUNCH(diff_combine_kernel<float>, blocks, 256, 0, stream, in, in_stride, (float*)out, out_stride, n_tokens, n_heads, per_group,
-              v_dim, lambda, eps, post);
+              v_dim, lambda, eps, post, tail);
   else if (dtype == BN_BF16)
     BN_LAUNCH(diff_combine_kernel<__nv_bfloat16>, blocks, 256, 0, stream, in, in_stride, (__nv_bfloat16*)out, out_stride, n_tokens,
-              n_heads, per_group, v_dim, lambda, eps, post);
+              n_heads, per_group, v_dim, lambda, eps, post, tail);
   else
     return BN_ERR_BAD_ARG;
   BN_CHECK_LAUNCH();

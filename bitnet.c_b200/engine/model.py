@@ -236,14 +236,26 @@ class Model:
     def forward(self, cache: Cache, ctx: StepContext) -> Optional[torch.Tensor]:
         """Embedding, every scheduled run, final norm and head at the wanted rows."""
         x = torch.empty((ctx.n_tokens, self.spec.width), dtype=torch.float32, device=self.device)
-        ops.embed_gather(self.embedding, ctx.tokens, x, self._bad_token, self.spec.embedding_scale)
-        if self.embedding_norm is not None:  # the stream starts as the normed embedding rows
+        sched = self.spec.schedule
+        pending = None
+        if self.embedding_norm is None:
+            ops.embed_gather(self.embedding, ctx.tokens, x, self._bad_token, self.spec.embedding_scale)
+        elif self.spec.width > ops.EMBED_NORMED_MAX_WIDTH:
+            ops.embed_gather(self.embedding, ctx.tokens, x, self._bad_token, self.spec.embedding_scale)
             ops.scaled_add_rmsnorm(x, 1.0, None, self.embedding_norm.weight, self.embedding_norm.spec.eps)
+        else:
+            # the stream starts as the normed embedding rows; the first block's first norm is taken in the same pass
+            # when that block says which it is
+            first = self.blocks[sched[0].block]
+            reader = first.entry_norm() if getattr(first, "accepts_normed", False) else None
+            w1 = getattr(reader, "weight", None) if reader is not None else None
+            h = ops.embed_gather_normed(self.embedding, ctx.tokens, x, self._bad_token, self.spec.embedding_scale,
+                                        self.embedding_norm.weight, self.embedding_norm.spec.eps, w1,
+                                        reader.spec.eps if w1 is not None else 0.0, self.dtype)
+            pending = Normed(h) if h is not None else None
         diag = ctx.diag = self.diagnostics
         ctx.layer = -1
         ctx.tap("inp", x)
-        pending = None
-        sched = self.spec.schedule
         for i, e in enumerate(sched):
             blk = self.blocks[e.block]
             if isinstance(pending, Cast) and not getattr(blk, "accepts_cast", False):

@@ -93,7 +93,11 @@ class Moe(FeedForward):
         T = h.shape[0]
         shared = self._expert(h, self.w_shared_gate_up, self.w_shared_down, s.shared_limit, torch.float32) if s.shared_ff else None
         if self.by_table:
-            ids, weights = ops.moe_table_route(ctx.tokens, self.table, s.top, s.n_experts)
+            # the choice depends on the step's token ids alone: runs that share a table share its rows of the step
+            key = ("moe.table", self.table.data_ptr(), s.top)
+            if key not in ctx.memo:
+                ctx.memo[key] = ops.moe_table_route(ctx.tokens, self.table, s.top, s.n_experts)
+            ids, weights = ctx.memo[key]
         else:
             ids, weights = ops.moe_route(h, self.w_router, s.top, s.renormalise, softmax=self.softmax,
                                          weight_scale=getattr(s, "weight_scale", 1.0), sum_eps=getattr(s, "renormalise_eps", 0.0))

@@ -105,6 +105,15 @@ class NormedAttention(Mixer):
             self.b_in[self.v_off: self.v_off + self.v_len] = tensors["v.b"].float()
         self.w_o = tensors["o"]
         self.b_o = tensors["o.b"].float().contiguous() if s.out_bias else None
+        self.tail = 0
+        if s.out_bias and s.maps == 2:
+            # the output bias as a column of the output matrix: the kernel that combines the maps leaves a one behind
+            # the heads of every row (and zeros up to a 16-byte boundary), so the product adds the bias itself
+            self.tail = 8
+            extra = torch.zeros((s.width, self.tail), dtype=self.w_o.dtype, device=dev)
+            extra[:, 0] = tensors["o.b"].to(self.w_o.dtype)
+            self.w_o = torch.cat([self.w_o, extra], dim=1).contiguous()
+            self.b_o = None
         self.wq = self.wk = None
         self.q_span = self.k_span = 0
         if s.qk_norm == "head":
@@ -163,8 +172,8 @@ class NormedAttention(Mixer):
                                   v_share=s.maps, max_keys=min(ctx.max_len, s.window) if s.window > 0 else ctx.max_len)
         if s.maps == 2:
             both = out
-            out = torch.empty((n, s.n_heads * s.v_head_dim), dtype=dt, device=dev)
-            ops.diff_combine(both, out, s.n_heads, self.per_group, s.v_head_dim, self.lam, s.norm_eps, 1.0 - s.diff)
+            out = torch.empty((n, s.n_heads * s.v_head_dim + self.tail), dtype=dt, device=dev)
+            ops.diff_combine(both, out, s.n_heads, self.per_group, s.v_head_dim, self.lam, s.norm_eps, 1.0 - s.diff, tail=self.tail)
         ctx.tap("attn_out", out)
         d = ops.linear(out, self.w_o, out_dtype=torch.float32)
         if self.b_o is not None:

@@ -213,8 +213,9 @@ def experts_by_table(h, tokens, w, p, f, r=_id):
 
 # ---- the model -----------------------------------------------------------------------------------------
 def layer_prefix(cfg, i: int) -> str:
-    j = cfg["layers"][i].get("weights_of")
-    return f"l{i if j is None else int(j)}."
+    while cfg["layers"][i].get("weights_of") is not None:
+        i = int(cfg["layers"][i]["weights_of"])
+    return f"l{i}."
 
 
 def layer(x, tokens, w, cfg, i, r=_id):

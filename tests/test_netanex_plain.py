@@ -230,6 +230,7 @@ def test_mixers_carry_every_constant_of_the_configuration():
     (lambda c: c["layers"][0].update(type="attention_3"), "type"),
     (lambda c: c["layers"][0]["mixer"].update(heads=5), "multiple"),
     (lambda c: c["layers"][2]["mixer"].update(rot_dim=6), "rot"),
+    (lambda c: c["layers"][3]["mixer"].update(rot_dim=10), "differs"),
     (lambda c: c["layers"][3].update(weights_of=4), "weights_of"),
     (lambda c: c["layers"][4]["mixer"].update(diff=0.1), "differs"),
     (lambda c: c["layers"][0]["mlp"]["router"].update(top=9), "top"),
