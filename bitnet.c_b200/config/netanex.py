@@ -1,7 +1,7 @@
 """Netanex: a decoder whose layers are listed one by one in ``config.json``.
 
 The embedding row of a token is normed; every layer is a block with a norm before and after each sublayer,
-x <- x + n1b(mixer(n1(x))), x <- x + n2b(ffn(n2(x))), all four RMS norms with a gain stored around zero
+x <- x + n1b(mixer(n1(x))), x <- x + n2b(ffn(n2(x))), all four RMS norms with a gain kept as its offset from one
 (the factor is 1 + w).  Three mixers: ``attention`` (grouped-query attention with two maps of scores per
 head over the same values, the second subtracted with a learned factor; queries and keys normed per head and
 map; queries that grow with the logarithm of the position; biases on all four projections), ``attention_2``

@@ -27,7 +27,7 @@ class RmsNormSpec:
     eps: float
     kind: str = "rmsnorm"
     optional: bool = False  # the file may lack the gain; the norm is then not applied by who owns it
-    one_plus: bool = False  # the stored gain sits around zero: the factor is 1 + w
+    one_plus: bool = False  # the file holds the gain minus one: the factor is 1 + w
 
 
 @dataclass(frozen=True)

@@ -26,7 +26,7 @@ class RmsNorm(Norm):
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         self.weight = tensors["weight"]
         if self.weight is not None and getattr(self.spec, "one_plus", False):
-            # a gain stored around zero: the factor 1 + w, made once in float32 (in bfloat16 the sum would lose the
+            # a gain kept as its offset from one: the factor 1 + w, made once in float32 (in bfloat16 the sum would lose the
             # stored gain's low bits); the kernels read gains of either type
             self.weight = (1.0 + self.weight.float()).contiguous()
 

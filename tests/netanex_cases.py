@@ -3,7 +3,7 @@
 The weights are drawn here, by tensor name and shape as the design names them (not from the library's
 parameter table), with scales that make faults show: after their norms queries and keys have components of
 size one, so with scales of about 2 / sqrt(dim) the scores spread over several units; sinks around three, so
-that a softmax without them is visibly another; gains stored around zero of size 0.2; biases of size one
+that a softmax without them is visibly another; gains whose stored offsets from one are of size 0.2; biases of size one
 half; gates' pre-activations of size two; the four vectors behind the second map's factor large enough that
 the factor is far from the constant it would be without them.  All values are exactly representable in
 bfloat16, so the same folder serves both number formats.
@@ -147,7 +147,7 @@ def draw_weights(cfg: dict, seed: int) -> dict:
         if name.endswith((".q.norm", ".k.norm", ".dkv.norm")):
             a = 1.0 + 0.2 * rng.standard_normal(shape)
         elif last in ("norm1", "norm1b", "norm2", "norm2b", "norm"):
-            a = 0.2 * rng.standard_normal(shape)  # stored around zero
+            a = 0.2 * rng.standard_normal(shape)  # the offset from one
         elif last == "embed":
             a = rng.standard_normal(shape)
         elif last == "sink":

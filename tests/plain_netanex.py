@@ -2,7 +2,7 @@
 whole sequences, no cache, no batching.  It shares no code with the library under test.
 
 The design: the embedding row of a token, normed; layers x <- x + n1b(mixer(n1(x))), x <- x + n2b(ff(n2(x)))
-whose four norms are RMS norms with a gain stored around zero (the factor is 1 + w); three mixers
+whose four norms are RMS norms with a gain kept as its offset from one (the factor is 1 + w); three mixers
 (differential attention: two softmax maps per head over the same values, the second subtracted with a
 learned factor, queries growing with the logarithm of the position; attention through a cached low-rank
 latent with a rotated key part shared by all heads, a sliding window, a learned sink in the softmax's
@@ -41,7 +41,7 @@ def rms(x: np.ndarray, eps: float) -> np.ndarray:
 
 
 def norm_one_plus(x, w, eps):
-    """The layers' norm: the stored gain sits around zero."""
+    """The layers' norm: the file holds the gain minus one."""
     return rms(x, eps) * (1.0 + w)
 
 

@@ -288,7 +288,7 @@ def test_random_weights_of_the_design_have_tables_of_different_experts(tmp_path)
         assert set(f.names()) == set(nc.tensor_shapes(nc.CASE_C))
         t = f.read("l2.mlp.table").numpy()
         assert t.shape == (150, 3) and t.min() >= 0 and t.max() < 4 and all(len(set(row)) == 3 for row in t)
-        assert abs(float(f.read("l0.norm1").float().mean())) < 0.1  # gains are stored around zero
+        assert abs(float(f.read("l0.norm1").float().mean())) < 0.1  # gains are kept as offsets from one
     finally:
         f.close()
     assert json.load(open(tmp_path / "m" / "config.json"))["architecture"] == "Netanex"
