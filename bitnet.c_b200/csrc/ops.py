@@ -1398,7 +1398,8 @@ def rotary_pairs_append(x: torch.Tensor, freqs: torch.Tensor, tok_pos: torch.Ten
                         tok_seq: Optional[torch.Tensor] = None, slots: Optional[torch.Tensor] = None,
                         page_table: Optional[torch.Tensor] = None, k_cache: Optional[torch.Tensor] = None,
                         v_cache: Optional[torch.Tensor] = None, norm_len: int = 0, norm_w: Optional[torch.Tensor] = None,
-                        norm_eps: float = 0.0, split_halves: bool = False, magnitude: float = 1.0) -> None:
+                        norm_eps: float = 0.0, split_halves: bool = False, magnitude: float = 1.0,
+                        freqs64: Optional[torch.Tensor] = None) -> None:
     """Rotary encoding in place: in every row of x the pairs (2i, 2i + 1), i < len(freqs) (with ``split_halves``
     the pairs (i, i + len(freqs)); cos and sin both times ``magnitude``),
     of the rotated part of each query head (heads ``q_head_stride`` apart from ``q_off``, the part at ``q_rot_off``
@@ -1414,6 +1415,10 @@ def rotary_pairs_append(x: torch.Tensor, freqs: torch.Tensor, tok_pos: torch.Ten
     if xq.shape[0] < tok_pos.shape[0]:
         raise KernelError("rotary_pairs_append: xq has fewer rows than there are tokens")
     _need(freqs, "freqs", torch.float32, 1)
+    if freqs64 is not None:  # the same table in double precision: angles are then taken in double precision too
+        _need(freqs64, "freqs64", torch.float64, 1)
+        if freqs64.shape[0] != freqs.shape[0]:
+            raise KernelError("rotary_pairs_append: both tables hold one frequency per pair")
     _need(tok_pos, "tok_pos", torch.int32, 1)
     n = tok_pos.shape[0]
     if x.shape[0] < n:
@@ -1442,7 +1447,7 @@ def rotary_pairs_append(x: torch.Tensor, freqs: torch.Tensor, tok_pos: torch.Ten
         int(n_q_heads), int(q_head_stride), int(q_rot_off), int(k_off), int(n_k_heads), int(k_head_stride), int(k_rot_off),
         int(k_row), int(v_off), int(v_head_stride), int(v_row), _ptr(tok_seq), _ptr(slots), _ptr(page_table), int(pt_stride),
         _ptr(k_cache), _ptr(v_cache), int(norm_len), _ptr(norm_w), int(_code(norm_w)) if norm_w is not None else 0,
-        c_float(norm_eps), int(bool(split_halves)), c_float(magnitude), _stream()), "rotary_pairs_append")
+        c_float(norm_eps), int(bool(split_halves)), c_float(magnitude), _ptr(freqs64), _stream()), "rotary_pairs_append")
 
 
 def residual_add(x: torch.Tensor, a: torch.Tensor, b: Optional[torch.Tensor] = None,

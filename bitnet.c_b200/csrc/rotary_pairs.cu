@@ -3,7 +3,8 @@
 //
 // Dimension 2i of the rotated part of a head is paired with dimension 2i + 1 (or, with split_halves,
 // dimension i with dimension i + half); at position p the pair (u, v) becomes
-// (u cos a - v sin a, v cos a + u sin a) with a = p * freq[i] in float32, cos and sin both times `magnitude`.  The
+// (u cos a - v sin a, v cos a + u sin a) with a = p * freq[i] in float32 (in double precision when the table comes
+// as doubles, freqs64), cos and sin both times `magnitude`.  The
 // frequencies come as a table, so that whoever builds it decides base, scaling of long
 // wavelengths and the like (parts/position.py).  The rotated part may lie anywhere inside a head
 // (rot_off), so heads of the form [plain | rotated] and keys whose last numbers are a rotated part
@@ -28,7 +29,8 @@ __global__ void rotary_pairs_append_kernel(T* xq, int q_row_stride, T* xk, int r
                                            const int* __restrict__ tok_seq, const int* __restrict__ slots,
                                            const int* __restrict__ page_table, int pt_stride, T* __restrict__ k_cache,
                                            T* __restrict__ v_cache, int norm_len, const void* __restrict__ norm_w,
-                                           int norm_w_dtype, float norm_eps, int split_halves, float magnitude) {
+                                           int norm_w_dtype, float norm_eps, int split_halves, float magnitude,
+                                           const double* __restrict__ freqs64) {
   pdl_launch_dependents();
   pdl_wait();
   __shared__ float cs[RP_MAX_HALF], sn[RP_MAX_HALF];
@@ -39,7 +41,16 @@ __global__ void rotary_pairs_append_kernel(T* xq, int q_row_stride, T* xk, int r
   T* qrow = xq + (size_t)t * q_row_stride;  // the row that holds the query heads (may be the same)
   for (int i = threadIdx.x; i < half; i += blockDim.x) {
     float sv, cv;
-    sincosf((float)pos * freqs[i], &sv, &cv);
+    if (freqs64) {
+      // the table in double precision: the angle is taken there too (at position p a float32 angle is off by up to
+      // p * 6e-8 radians), a few hundred values per token
+      double sd, cd;
+      sincos((double)pos * freqs64[i], &sd, &cd);
+      sv = (float)sd;
+      cv = (float)cd;
+    } else {
+      sincosf((float)pos * freqs[i], &sv, &cv);
+    }
     sn[i] = sv * magnitude;
     cs[i] = cv * magnitude;
   }
@@ -96,7 +107,7 @@ extern "C" int bn_rotary_pairs_append(void* xq, int q_row_stride, void* xk, int 
                                       int v_head_stride, int v_row, const int* tok_seq, const int* slots,
                                       const int* page_table, int pt_stride, void* k_cache, void* v_cache,
                                       int norm_len, const void* norm_w, int norm_w_dtype, float norm_eps,
-                                      int split_halves, float magnitude, cudaStream_t stream) {
+                                      int split_halves, float magnitude, const double* freqs64, cudaStream_t stream) {
   if (n <= 0) return BN_OK;
   if (norm_len < 0 || (norm_len > 0 && (!norm_w || n_k_heads != 1 || norm_len > k_rot_off || !(norm_eps > 0.f) ||
                                         (norm_w_dtype != BN_F32 && norm_w_dtype != BN_BF16))))
@@ -114,13 +125,13 @@ extern "C" int bn_rotary_pairs_append(void* xq, int q_row_stride, void* xk, int 
     BN_LAUNCH(rotary_pairs_append_kernel<float>, n, RP_THREADS, 0, stream, (float*)xq, q_row_stride, (float*)xk, row_stride, freqs, half, tok_pos, q_off,
               n_q_heads, q_head_stride, q_rot_off, k_off, n_k_heads, k_head_stride, k_rot_off, k_row, v_off, v_head_stride,
               v_row, tok_seq, slots, page_table, pt_stride, (float*)k_cache, (float*)v_cache, norm_len, norm_w, norm_w_dtype, norm_eps,
-              split_halves, magnitude);
+              split_halves, magnitude, freqs64);
   else if (dtype == BN_BF16)
     BN_LAUNCH(rotary_pairs_append_kernel<__nv_bfloat16>, n, RP_THREADS, 0, stream, (__nv_bfloat16*)xq, q_row_stride,
               (__nv_bfloat16*)xk, row_stride, freqs, half,
               tok_pos, q_off, n_q_heads, q_head_stride, q_rot_off, k_off, n_k_heads, k_head_stride, k_rot_off, k_row, v_off,
               v_head_stride, v_row, tok_seq, slots, page_table, pt_stride, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, norm_len,
-              norm_w, norm_w_dtype, norm_eps, split_halves, magnitude);
+              norm_w, norm_w_dtype, norm_eps, split_halves, magnitude, freqs64);
   else
     return BN_ERR_BAD_ARG;
   return BN_OK;

@@ -95,16 +95,16 @@ class RotaryPairs(Position):
         ops.rotary_pairs_append(x, self.freqs(x.device), ctx.tok_pos, **places)
 
 
-def blended_frequencies(spec):
+def blended_frequencies(spec, wide: bool = False):
     """(table, magnitude) of a ``RotaryBlendSpec``: base^(-2i/dims) for i < dims/2 in double precision, the slow
     ones divided by ``factor`` along a ramp between the dimension that turns ``fast`` times within ``original``
-    positions and the one that turns ``slow`` times; rounded to float32 once.  The magnitude multiplies cos and
-    sin alike."""
+    positions and the one that turns ``slow`` times; rounded to float32 once (``wide``: left in double precision).
+    The magnitude multiplies cos and sin alike."""
     dims = spec.dims
     i = np.arange(dims // 2, dtype=np.float64)
     f = np.float64(spec.base) ** (-2.0 * i / dims)
     if spec.factor == 1.0 or spec.original <= 0:
-        return f.astype(np.float32), 1.0
+        return (f if wide else f.astype(np.float32)), 1.0
 
     def turns(t):
         return dims * np.log(spec.original / (2.0 * np.pi * t)) / (2.0 * np.log(spec.base))
@@ -113,7 +113,7 @@ def blended_frequencies(spec):
     hi = min(int(np.ceil(turns(spec.slow))), dims - 1)
     ramp = np.clip((i - lo) / max(hi - lo, 0.001), 0.0, 1.0)
     f = f / spec.factor * ramp + f * (1.0 - ramp)
-    return f.astype(np.float32), float(spec.magnitude_slope * np.log(spec.factor) + 1.0)
+    return (f if wide else f.astype(np.float32)), float(spec.magnitude_slope * np.log(spec.factor) + 1.0)
 
 
 @register_position("rotary_blend")
@@ -130,13 +130,22 @@ class RotaryBlend(RotaryPairs):
         if spec.pairing not in ("halves", "neighbours"):
             raise ValueError(f"rotary pairing is 'halves' or 'neighbours', not {spec.pairing!r}")
         self._table, self.magnitude = blended_frequencies(spec)
-        self._freqs = None
+        self._table64 = blended_frequencies(spec, wide=True)[0]
+        self._freqs = self._freqs64 = None
         self.split_halves = spec.pairing == "halves"
+
+    def freqs64(self, device):
+        """The table in double precision: the kernel then takes the angles in double precision as well, so that a
+        position in the thousands costs no digits of the angle."""
+        if self._freqs64 is None or self._freqs64.device != device:
+            import torch
+            self._freqs64 = torch.from_numpy(np.ascontiguousarray(self._table64, dtype=np.float64)).to(device)
+        return self._freqs64
 
     def rotate(self, x, n_heads, head_dim, ctx):
         ops.rotary_pairs_append(x, self.freqs(x.device), ctx.tok_pos, q_off=0, n_q_heads=n_heads, q_head_stride=head_dim,
-                                split_halves=self.split_halves, magnitude=self.magnitude)
+                                split_halves=self.split_halves, magnitude=self.magnitude, freqs64=self.freqs64(x.device))
 
     def apply(self, x, ctx, **places):
         ops.rotary_pairs_append(x, self.freqs(x.device), ctx.tok_pos, split_halves=self.split_halves, magnitude=self.magnitude,
-                                **places)
+                                freqs64=self.freqs64(x.device), **places)
