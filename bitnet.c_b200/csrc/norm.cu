@@ -352,7 +352,9 @@ extern "C" int bn_residual_add_norms(float* x, const void* a, int a_dtype, const
 
 // x += y / sqrt(mean(y^2) + eps_y) * wy: a delta that enters the stream through a norm of its own.
 // Then, if `w` is given, out[r] = x * rsqrt(mean(x^2) + eps) * w: the norm that reads the stream next,
-// in the same pass (out in the compute type).  One block per row; float32 statistics.
+// in the same pass (out in the compute type).  One block per row; float32 statistics.  VEC: rows of whole
+// 16-byte pieces at aligned addresses are read and written four numbers at a time.
+template <bool VEC>
 __global__ void add_normed_kernel(float* __restrict__ x, const void* __restrict__ y, int y_dtype,
                                   const void* __restrict__ wy, int wy_dtype, float eps_y, const void* __restrict__ w,
                                   int w_dtype, float eps, void* __restrict__ out, int out_dtype, int width) {
@@ -362,6 +364,37 @@ __global__ void add_normed_kernel(float* __restrict__ x, const void* __restrict_
   float* scratch = v + width;
   const size_t row = blockIdx.x;
   float* xr = x + row * width;
+  if (VEC) {
+    const int n4 = width >> 2;
+    const size_t r4 = row * n4;
+    float4* v4 = reinterpret_cast<float4*>(v);
+    float4* x4 = reinterpret_cast<float4*>(xr);
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < n4; i += blockDim.x) {
+      const float4 a = load4_as_f32(y, y_dtype, (r4 + i) * 4);
+      v4[i] = a;
+      ss += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
+    }
+    ss = block_sum(ss, scratch);
+    const float scale_y = 1.0f / sqrtf(ss / (float)width + eps_y);
+    float sx = 0.f;
+    for (int i = threadIdx.x; i < n4; i += blockDim.x) {
+      const float4 g = load4_as_f32(wy, wy_dtype, (size_t)i * 4), b = v4[i];
+      float4 a = x4[i];
+      a.x += b.x * scale_y * g.x; a.y += b.y * scale_y * g.y; a.z += b.z * scale_y * g.z; a.w += b.w * scale_y * g.w;
+      x4[i] = a;
+      v4[i] = a;
+      sx += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
+    }
+    if (!w) return;
+    sx = block_sum(sx, scratch);
+    const float scale = 1.0f / sqrtf(sx / (float)width + eps);
+    for (int i = threadIdx.x; i < n4; i += blockDim.x) {
+      const float4 g = load4_as_f32(w, w_dtype, (size_t)i * 4), a = v4[i];
+      store4_from_f32(out, out_dtype, (r4 + i) * 4, make_float4(a.x * scale * g.x, a.y * scale * g.y, a.z * scale * g.z, a.w * scale * g.w));
+    }
+    return;
+  }
   float ss = 0.f;
   for (int i = threadIdx.x; i < width; i += blockDim.x) {
     float a = load_as_f32(y, y_dtype, row * width + i);
@@ -390,17 +423,23 @@ extern "C" int bn_add_normed(float* x, const void* y, int y_dtype, const void* w
   if (width <= 0 || !(eps_y > 0.f) || !x || !y || !wy || (w && (!out || !(eps > 0.f)))) return BN_ERR_BAD_ARG;
   size_t smem = ((size_t)width + 32) * sizeof(float);
   if (smem > 200 * 1024) return BN_ERR_BAD_ARG;
+  const bool vec = width % 4 == 0 && !(((uintptr_t)x | (uintptr_t)y | (uintptr_t)wy | (uintptr_t)w | (uintptr_t)out) & 15);
   if (smem > 48 * 1024) {
     static size_t granted = 0;
     if (smem > granted) {
-      cudaError_t e = cudaFuncSetAttribute(add_normed_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      cudaError_t e = cudaFuncSetAttribute(add_normed_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e == cudaSuccess) e = cudaFuncSetAttribute(add_normed_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (e != cudaSuccess) return BN_ERR_LAUNCH + (int)e;
       granted = smem;
     }
   }
   int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
-  BN_LAUNCH(add_normed_kernel, n_rows, threads, smem, stream, x, y, y_dtype, wy, wy_dtype, eps_y, w, w_dtype, eps, out,
-            out_dtype, width);
+  if (vec)
+    BN_LAUNCH(add_normed_kernel<true>, n_rows, threads, smem, stream, x, y, y_dtype, wy, wy_dtype, eps_y, w, w_dtype, eps, out,
+              out_dtype, width);
+  else
+    BN_LAUNCH(add_normed_kernel<false>, n_rows, threads, smem, stream, x, y, y_dtype, wy, wy_dtype, eps_y, w, w_dtype, eps, out,
+              out_dtype, width);
   return BN_OK;
 }
 

@@ -166,7 +166,29 @@ extern "C" int bn_slice_norm_append(void* x, int dtype, int n_tokens, int row_st
 // A span of head_dim numbers norms every head by itself with one gain for all heads; a span of the whole slice
 // norms all heads of a token at once.  Span 0: no norm.  every 0: no factor.  The value plane may have fewer heads
 // than the key plane (n_v_heads).  One block per token; the row waits in shared memory between the phases.
+// VEC: every slice, span and head begins and ends at a multiple of four numbers and all addresses are multiples of
+// 16 bytes, so rows are read, written and placed into the pages four numbers at a time.
 template <typename T>
+__device__ __forceinline__ void store4(T* p, float4 v);
+template <>
+__device__ __forceinline__ void store4<float>(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+template <>
+__device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16* p, float4 v) {
+  const __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+  uint2 raw;
+  raw.x = *reinterpret_cast<const unsigned*>(&a);
+  raw.y = *reinterpret_cast<const unsigned*>(&b);
+  *reinterpret_cast<uint2*>(p) = raw;
+}
+__device__ __forceinline__ float4 gain4(const void* w, int dtype, int i) {
+  if (dtype == BN_F32) return *reinterpret_cast<const float4*>((const float*)w + i);
+  const uint2 raw = *reinterpret_cast<const uint2*>((const __nv_bfloat16*)w + i);
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+
+template <typename T, bool VEC>
 __global__ void qk_norm_append_kernel(const float* __restrict__ src, int src_stride, const void* __restrict__ bias, int bias_dtype,
                                       T* __restrict__ out, int out_stride, int row_len, int q_len, int q_span,
                                       const void* __restrict__ wq, int k_off, int k_len, int k_span, const void* __restrict__ wk,
@@ -182,7 +204,18 @@ __global__ void qk_norm_append_kernel(const float* __restrict__ src, int src_str
   const int t = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
   const float* s = src + (size_t)t * src_stride;
-  for (int i = threadIdx.x; i < row_len; i += blockDim.x) qk_row[i] = s[i] + (bias ? load_as_f32(bias, bias_dtype, i) : 0.f);
+  if (VEC) {
+    for (int i = threadIdx.x * 4; i < row_len; i += blockDim.x * 4) {
+      float4 a = *reinterpret_cast<const float4*>(s + i);
+      if (bias) {
+        const float4 b = gain4(bias, bias_dtype, i);
+        a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+      }
+      *reinterpret_cast<float4*>(qk_row + i) = a;
+    }
+  } else {
+    for (int i = threadIdx.x; i < row_len; i += blockDim.x) qk_row[i] = s[i] + (bias ? load_as_f32(bias, bias_dtype, i) : 0.f);
+  }
   __syncthreads();
   const int nq = q_span > 0 ? q_len / q_span : 0, nk = k_span > 0 ? k_len / k_span : 0;
   for (int g = warp; g < nq + nk; g += n_warps) {
@@ -200,6 +233,39 @@ __global__ void qk_norm_append_kernel(const float* __restrict__ src, int src_str
   const int* pt = k_cache ? page_table + (size_t)slots[tok_seq[t]] * pt_stride : nullptr;
   T* o = out + (size_t)t * out_stride;
   const int v_len = n_v_heads * v_dim;
+  if constexpr (VEC) {
+    for (int i = threadIdx.x * 4; i < row_len; i += blockDim.x * 4) {
+      float4 a = *reinterpret_cast<const float4*>(qk_row + i);
+      if (i < q_len) {
+        float f = temp;
+        if (q_span > 0) {
+          const float4 g = gain4(wq, w_dtype, i % q_span);
+          f *= inv[i / q_span];
+          a.x *= g.x; a.y *= g.y; a.z *= g.z; a.w *= g.w;
+        }
+        a.x *= f; a.y *= f; a.z *= f; a.w *= f;
+        store4<T>(o + i, a);
+      } else if (i >= k_off && i < k_off + k_len) {
+        const int j = i - k_off;
+        if (k_span > 0) {
+          const float4 g = gain4(wk, w_dtype, j % k_span);
+          const float f = inv[nq + j / k_span];
+          a.x *= g.x * f; a.y *= g.y * f; a.z *= g.z * f; a.w *= g.w * f;
+        }
+        store4<T>(o + i, a);
+        if (k_cache) {
+          const int kvh = j / head_dim, d = j - kvh * head_dim;
+          store4<T>(k_cache + cache_row_offset(pt, pos, n_kv_heads, kvh, head_dim) + d, a);
+        }
+      } else {
+        store4<T>(o + i, a);
+        if (v_cache && i >= v_off && i < v_off + v_len) {
+          const int j = i - v_off, vh = j / v_dim, d = j - vh * v_dim;
+          store4<T>(v_cache + cache_row_offset(pt, pos, n_v_heads, vh, v_dim) + d, a);
+        }
+      }
+    }
+  } else {
   for (int i = threadIdx.x; i < row_len; i += blockDim.x) {
     float a = qk_row[i];
     if (i < q_len) {
@@ -224,6 +290,7 @@ __global__ void qk_norm_append_kernel(const float* __restrict__ src, int src_str
       }
     }
   }
+  }
 }
 
 extern "C" int bn_qk_norm_append(const float* src, int src_stride, const void* bias, int bias_dtype, void* out, int dtype, int out_stride,
@@ -241,25 +308,36 @@ extern "C" int bn_qk_norm_append(const float* src, int src_stride, const void* b
   const int spans = (q_span > 0 ? q_len / q_span : 0) + (k_span > 0 ? k_len / k_span : 0);
   const size_t smem = ((size_t)row_len + spans) * sizeof(float);
   if (smem > 200 * 1024) return BN_ERR_BAD_ARG;
+  // four numbers at a time when nothing begins or ends inside a group of four and every address is a multiple of 16 bytes
+  const bool vec = !((row_len | src_stride | out_stride | q_len | k_off | k_len | v_off | q_span | k_span) & 3) &&
+                   (!k_cache || !((head_dim | v_dim) & 3)) &&
+                   !(((uintptr_t)src | (uintptr_t)bias | (uintptr_t)out | (uintptr_t)wq | (uintptr_t)wk | (uintptr_t)k_cache |
+                      (uintptr_t)v_cache) & 15);
+#define BN_QK_LAUNCH(TT, VV)                                                                                                   \
+  BN_LAUNCH((qk_norm_append_kernel<TT, VV>), n_tokens, UN_THREADS, smem, stream, src, src_stride, bias, bias_dtype, (TT*)out,  \
+            out_stride, row_len, q_len, q_span, wq, k_off, k_len, k_span, wk, w_dtype, eps, temp_coef, temp_every, v_off,      \
+            n_kv_heads, head_dim, n_v_heads, v_dim, tok_seq, tok_pos, slots, page_table, pt_stride, (TT*)k_cache,              \
+            (TT*)v_cache)
 #define BN_QK_PREP(TT)                                                                                                         \
   do {                                                                                                                         \
     if (smem > 48 * 1024) {                                                                                                    \
       static size_t granted = 0;                                                                                               \
       if (smem > granted) {                                                                                                    \
-        cudaError_t e = cudaFuncSetAttribute(qk_norm_append_kernel<TT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        cudaError_t e = cudaFuncSetAttribute(qk_norm_append_kernel<TT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        if (e == cudaSuccess)                                                                                                  \
+          e = cudaFuncSetAttribute(qk_norm_append_kernel<TT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
         if (e != cudaSuccess) return BN_ERR_LAUNCH + (int)e;                                                                   \
         granted = smem;                                                                                                        \
       }                                                                                                                        \
     }                                                                                                                          \
-    BN_LAUNCH(qk_norm_append_kernel<TT>, n_tokens, UN_THREADS, smem, stream, src, src_stride, bias, bias_dtype, (TT*)out,      \
-              out_stride, row_len, q_len, q_span, wq, k_off, k_len, k_span, wk, w_dtype, eps, temp_coef, temp_every, v_off,    \
-              n_kv_heads, head_dim, n_v_heads, v_dim, tok_seq, tok_pos, slots, page_table, pt_stride, (TT*)k_cache,            \
-              (TT*)v_cache);                                                                                                   \
+    if (vec) BN_QK_LAUNCH(TT, true);                                                                                           \
+    else BN_QK_LAUNCH(TT, false);                                                                                              \
   } while (0)
   if (dtype == BN_F32) BN_QK_PREP(float);
   else if (dtype == BN_BF16) BN_QK_PREP(__nv_bfloat16);
   else return BN_ERR_BAD_ARG;
 #undef BN_QK_PREP
+#undef BN_QK_LAUNCH
   BN_CHECK_LAUNCH();
   return BN_OK;
 }
