@@ -172,9 +172,17 @@ class NetanexConfig:
             while d["layers"][j].get("weights_of") is not None:  # a layer that itself runs with another's weights
                 j = d["layers"][j]["weights_of"]
             other = blocks[block_of[j]]
-            if (block.mixer, block.ffn) != (other.mixer, other.ffn):
-                raise ConfigError(f"config.json: layers[{i}] uses the weights of layer {j} but its mixer or feed-forward differs from that layer's")
-            schedule.append(ScheduleEntry(block=block_of[j]))
+            if (block.mixer, block.ffn) == (other.mixer, other.ffn):
+                schedule.append(ScheduleEntry(block=block_of[j]))  # the same block once more, with a cache of its own
+                continue
+            if d["layers"][j]["type"] != layer["type"] or (ffn is None) != (other.ffn is None):
+                raise ConfigError(f"config.json: layers[{i}] uses the weights of layer {j} but is of another kind than that layer")
+            # the same tensors under other constants (a window, a scale): a block of its own whose parameters carry the
+            # owner's tensor names, so the file's tensors are read once and bound to both (sizes that do not fit the
+            # owner's tensors show when the weights are loaded)
+            schedule.append(ScheduleEntry(block=len(blocks)))
+            blocks.append(SandwichBlockSpec(mixer=block.mixer, ffn=block.ffn, mixer_norm=norm, mixer_post_norm=norm,
+                                            ffn_norm=block.ffn_norm, ffn_post_norm=block.ffn_post_norm, label=f"{j}@{i}"))
         spec = ModelSpec(vocab_size=self.vocab, width=self.width, blocks=tuple(blocks), schedule=tuple(schedule),
                          final_norm=norm, max_positions=self.max_positions, tie_embeddings=True, embedding_norm=norm,
                          head=LinearHeadSpec())
@@ -190,7 +198,7 @@ def tensor_name(path: str) -> str:
         return fixed[path]
     parts = path.split(".")
     if parts[0] == "blocks" and len(parts) >= 4:
-        i, role, rest = parts[1], parts[2], ".".join(parts[3:])
+        i, role, rest = parts[1].split("@")[0], parts[2], ".".join(parts[3:])  # "j@i": layer i's block on layer j's tensors
         norms = {"mixer_norm": "norm1", "mixer_post_norm": "norm1b", "ffn_norm": "norm2", "ffn_post_norm": "norm2b"}
         if role in norms and rest == "weight":
             return f"l{i}.{norms[role]}"

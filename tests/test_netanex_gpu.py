@@ -397,6 +397,16 @@ EDGES = {
         {"type": "attention", "mixer": {"heads": 4, "kv_heads": 4, "dim": 8, "vdim": 4, "scale": 0.6, "diff": 0.9,
                                         "q_temp": {"coef": 2.0, "every": 3}},
          "mlp": {"kind": "moe", "router": {"experts": 40, "top": 1}, "expert": {"ff": 8}}, "weights_of": 0}] * 3,
+    "shared weights under constants of their own": [
+        {"type": "latent_attention", "mixer": {"heads": 2, "dim": 8, "rot_dim": 8, "vdim": 8, "kv_rank": 16, "scale": 0.5,
+                                               "mask": {"size": 40}, "rot": {"base": 100.0, "dims": 8}},
+         "mlp": {"kind": "moe", "router": {"experts": 3, "top": 2}, "expert": {"ff": 8}}},
+        {"type": "latent_attention", "mixer": {"heads": 2, "dim": 8, "rot_dim": 8, "vdim": 8, "kv_rank": 16, "scale": 0.3,
+                                               "mask": {"size": 7}, "rot": {"base": 100.0, "dims": 4}},
+         "mlp": {"kind": "moe", "router": {"experts": 3, "top": 2}, "expert": {"ff": 8}}, "weights_of": 0},
+        {"type": "attention", "mixer": {"heads": 2, "kv_heads": 1, "dim": 8, "vdim": 8, "scale": 0.6, "diff": 0.3}, "mlp": None},
+        {"type": "attention", "mixer": {"heads": 2, "kv_heads": 1, "dim": 8, "vdim": 8, "scale": 0.6, "diff": 0.7,
+                                        "q_temp": {"coef": 1.0, "every": 9}}, "mlp": None, "weights_of": 2}],
     "all experts for every token": [
         {"type": "attention_2", "mixer": {"heads": 8, "kv_heads": 1, "dim": 4, "vdim": 12, "scale": 0.9},
          "mlp": {"kind": "moe", "router": {"experts": 6, "top": 6}, "expert": {"ff": 12}}}],

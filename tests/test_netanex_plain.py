@@ -212,6 +212,23 @@ def test_the_configuration_becomes_blocks_a_schedule_and_the_designs_tensor_name
         assert spec.tie_embeddings and spec.embedding_norm.one_plus and spec.final_norm.one_plus
 
 
+def test_a_layer_on_anothers_weights_may_have_constants_of_its_own():
+    from bitnet_c_b200.config import architecture_of
+    from bitnet_c_b200.engine.model import parameter_table
+    cfg = copy.deepcopy(nc.CASE_A)
+    cfg["layers"][3]["mixer"]["mask"]["size"] = 5  # the same tensors under another window
+    cfg["layers"][4]["mixer"]["diff"] = 0.1
+    arch = architecture_of(cfg)
+    spec = arch.to_spec(arch.read_config(cfg))
+    assert len(spec.blocks) == 6 and [e.block for e in spec.schedule] == [0, 1, 2, 3, 4, 5]
+    assert [b.label for b in spec.blocks] == ["0", "1", "2", "2@3", "1@4", "5"]
+    assert spec.blocks[3].mixer.window == 5 and spec.blocks[2].mixer.window == 37 and spec.blocks[4].mixer.diff == 0.1
+    table = parameter_table(spec)
+    names = {arch.tensor_name(p) for p in table}
+    assert names == set(nc.tensor_shapes(nc.CASE_A))  # no tensor more than the owners have
+    assert arch.tensor_name("blocks.2@3.mixer.sink") == "l2.mix.sink" and arch.tensor_name("blocks.1@4.ffn.table") == "l1.mlp.table"
+
+
 def test_mixers_carry_every_constant_of_the_configuration():
     from bitnet_c_b200.config import architecture_of
     arch = architecture_of(nc.CASE_A)
@@ -230,9 +247,8 @@ def test_mixers_carry_every_constant_of_the_configuration():
     (lambda c: c["layers"][0].update(type="attention_3"), "type"),
     (lambda c: c["layers"][0]["mixer"].update(heads=5), "multiple"),
     (lambda c: c["layers"][2]["mixer"].update(rot_dim=6), "rot"),
-    (lambda c: c["layers"][3]["mixer"].update(rot_dim=10), "differs"),
     (lambda c: c["layers"][3].update(weights_of=4), "weights_of"),
-    (lambda c: c["layers"][4]["mixer"].update(diff=0.1), "differs"),
+    (lambda c: c["layers"][4].update(type="attention_2"), "another kind"),
     (lambda c: c["layers"][0]["mlp"]["router"].update(top=9), "top"),
     (lambda c: c["layers"][1]["mixer"].pop("diff"), "diff"),
     (lambda c: c["norm"].update(eps=0), "eps"),
