@@ -56,6 +56,7 @@ class StepContext:
     host_pos0: List[int] = field(default_factory=list)  # loop over sequences there
     host_slots: List[int] = field(default_factory=list)
     host_rows: List[int] = field(default_factory=list)  # the packed rows whose logits are wanted
+    host_tokens: Optional[np.ndarray] = None  # the packed token ids on the host (None in steps built on the device)
     # diagnostics (engine/diagnostics.py): None unless the model was given some; ``layer`` is the
     # schedule entry that is running (-1 outside the layers)
     diag: Optional[object] = None
@@ -125,4 +126,4 @@ def pack_step(seqs: Sequence[SeqStep], lengths: Sequence[int], device) -> StepCo
         tile_seq=dev[t0:t0 + n_tiles], tile_row0=dev[t0 + n_tiles:t0 + 2 * n_tiles],
         wide_tile_seq=dev[w0:w0 + n_wide], wide_tile_row0=dev[w0 + n_wide:w0 + 2 * n_wide], host_new=new,
         host_pos0=list(lengths),
-        host_slots=[s.slot for s in seqs], host_rows=[int(r) for r in rows])
+        host_slots=[s.slot for s in seqs], host_rows=[int(r) for r in rows], host_tokens=tokens)

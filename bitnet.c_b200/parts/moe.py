@@ -3,6 +3,7 @@ from __future__ import annotations
 
 from typing import Dict
 
+import numpy as np
 import torch
 
 from ..csrc import ops
@@ -74,6 +75,8 @@ class Moe(FeedForward):
         dt = self.build.dtype
         self.w_router = tensors.get("router")
         self.table = tensors.get("table")
+        # the table on the host too: how many tokens of a step take each expert is then known without asking the device
+        self.table_host = self.table.cpu().numpy() if self.table is not None else None
         # [experts, 2 ff, width]: an expert's gate rows, then its up rows; [experts, width, ff]
         self.w_gate_up = torch.stack([torch.cat([tensors[f"e{e}.gate"].to(dt), tensors[f"e{e}.up"].to(dt)], dim=0)
                                       for e in range(s.n_experts)]).contiguous()
@@ -107,7 +110,19 @@ class Moe(FeedForward):
             return ops.moe_experts_few(h, ids, weights, self.w_gate_up, self.w_down, s.expert_limit, s.slope,
                                        s.weight_on_input, add=shared, act=self.act)
         counts = ops.moe_count(ids, s.n_experts)
-        per_expert = counts.cpu().tolist()  # the one place where the host waits for the device
+        host_tokens = getattr(ctx, "host_tokens", None)
+        if self.by_table and host_tokens is not None:
+            # chosen by token id: the counts follow from the step's ids on the host, nobody waits for the device
+            ckey = ("moe.table.counts", self.table.data_ptr(), s.top)
+            if ckey not in ctx.memo:
+                rows = self.table_host.shape[0]
+                chosen = self.table_host[np.clip(host_tokens, 0, rows - 1), : s.top]
+                known = ((host_tokens >= 0) & (host_tokens < rows))[:, None] & (chosen >= 0) & (chosen < s.n_experts)
+                chosen = np.where(known, chosen, 0)  # what the kernel cannot place goes to expert 0 with weight 0
+                ctx.memo[ckey] = np.bincount(chosen.ravel(), minlength=s.n_experts).tolist()
+            per_expert = ctx.memo[ckey]
+        else:
+            per_expert = counts.cpu().tolist()  # the one place where the host waits for the device
         dt, dev_ = self.build.dtype, h.device
         cap = -(-max(per_expert) // 8) * 8
         if cap * s.n_experts <= self.PAD_FACTOR * T * s.top:
